@@ -1,0 +1,618 @@
+// Causal attention over a paged key/value cache for one head size (compile with -DLSE_HEAD_DIM=D,
+// D a multiple of 16, at most 256).
+//
+// For a query at absolute position p of a sequence, with keys j of the same sequence:
+//   s_j = scale * q . k_j   for  max(0, p - window + 1) <= j <= p   (window 0: from 0)
+//   o   = sum_j softmax(s)_j * v_j
+// Query head h reads key/value head h / (num_heads / num_kv_heads). Scores, the running maximum,
+// the normaliser and the weighted sum are float32 (src/llmserve/kernels/csrc/
+// paged_attention.cpp:191-243 does the same on the CPU). Keys and values are read from pages
+// [page][kv_head][offset][D] through the sequence's block table; nothing at or beyond a sequence's
+// context length is ever read, so pages that another request used before need no clearing.
+//
+// Three kernels:
+//   prefill_simt  portions of >= 2 rows, any dtype: 32 rows per block, 4 threads per row.
+//   prefill_mma   bfloat16 portions, D <= 128: 64 rows per block on mma.sync tensor cores.
+//   decode_split  single rows: the context is cut into partitions, one block per (partition,
+//                 head group, sequence); partial (max, sum, weighted values) are merged by
+//                 decode_merge (src/llmserve/kernels/csrc/paged_attention.cpp:245-346).
+#include "attention_args.h"
+#include "common.cuh"
+#include "kernels.h"
+
+#ifndef LSE_HEAD_DIM
+#error "compile with -DLSE_HEAD_DIM=<head size>"
+#endif
+
+namespace lse {
+
+constexpr int D = LSE_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+
+template <typename T>
+struct Exp;
+template <>
+struct Exp<float> {
+  __device__ __forceinline__ static float f(float x) { return expf(x); }
+};
+template <>
+struct Exp<bf16> {
+  __device__ __forceinline__ static float f(float x) { return __expf(x); }
+};
+
+__host__ __device__ constexpr int pow2_ceil(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
+struct SeqInfo {
+  int q_start, q_len, ctx, pos0;
+};
+
+__device__ __forceinline__ SeqInfo seq_info(const LseAttnArgs& a, int seq) {
+  SeqInfo s;
+  s.q_start = a.cu_q[seq];
+  s.q_len = a.cu_q[seq + 1] - s.q_start;
+  s.ctx = a.ctx_lens[seq];
+  s.pos0 = s.ctx - s.q_len;
+  return s;
+}
+
+// ============================================================================ prefill, CUDA cores
+constexpr int SIMT_QT = 32;
+constexpr int SIMT_KT = (D <= 128) ? 32 : 16;
+
+template <typename T>
+__global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, int page_shift) {
+  constexpr int QT = SIMT_QT, KT = SIMT_KT, DPT = D / 4, VEC = Num<T>::kVec, NCHUNK = D / VEC;
+  __shared__ float ks[KT][D];
+  __shared__ float vs[KT][D];
+  const int seq = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
+  const int head = blockIdx.y;
+  const int kvh = head / (a.num_heads / a.num_kv_heads);
+  const SeqInfo si = seq_info(a, seq);
+  const int r = threadIdx.x >> 2, sub = threadIdx.x & 3;
+  const int qi = q0 + r;
+  const bool row_valid = qi < si.q_len;
+  const int qpos = si.pos0 + qi;
+  const T* q = (const T*)a.q + (size_t)(si.q_start + (row_valid ? qi : 0)) * a.q_row_stride +
+               (size_t)head * D;
+  float qreg[DPT], acc[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    qreg[i] = Num<T>::to_float(q[sub + 4 * i]) * a.scale;
+    acc[i] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  const int rows_here = min(QT, si.q_len - q0);
+  const int k_end = si.pos0 + q0 + rows_here;  // one past the last key any row of the tile reads
+  const int k_first = a.window > 0 ? max(0, si.pos0 + q0 - a.window + 1) : 0;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const T* kp = (const T*)a.k_pages;
+  const T* vp = (const T*)a.v_pages;
+
+  for (int k0 = (k_first / KT) * KT; k0 < k_end; k0 += KT) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < KT * NCHUNK; idx += blockDim.x) {
+      const int jj = idx / NCHUNK, c = idx - jj * NCHUNK;
+      const int j = k0 + jj;
+      Vec16<T> kv, vv;
+      if (j >= k_first && j < k_end) {
+        int pi, off;
+        page_of(j, a.page_tokens, page_shift, pi, off);
+        const size_t base =
+            (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D + c * VEC;
+        kv = load16(kp + base);
+        vv = load16(vp + base);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) kv.v[e] = vv.v[e] = Num<T>::from_float(0.f);
+      }
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        ks[jj][c * VEC + e] = Num<T>::to_float(kv.v[e]);
+        vs[jj][c * VEC + e] = Num<T>::to_float(vv.v[e]);
+      }
+    }
+    __syncthreads();
+    float s[KT];
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int jj = 0; jj < KT; ++jj) {
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) d = fmaf(qreg[i], ks[jj][sub + 4 * i], d);
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      const int j = k0 + jj;
+      const bool ok = row_valid && j <= qpos && j >= k_first &&
+                      (a.window <= 0 || j > qpos - a.window);
+      s[jj] = ok ? d : -INFINITY;
+      tile_max = fmaxf(tile_max, s[jj]);
+    }
+    const float m_new = fmaxf(m, tile_max);
+    if (m_new == -INFINITY) continue;  // nothing visible yet for this row (uniform per 4 threads)
+    const float corr = Exp<T>::f(m - m_new);  // m = -inf gives 0
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) acc[i] *= corr;
+#pragma unroll
+    for (int jj = 0; jj < KT; ++jj) {
+      const float p = Exp<T>::f(s[jj] - m_new);  // s = -inf gives 0
+      l += p;
+#pragma unroll
+      for (int i = 0; i < DPT; ++i) acc[i] = fmaf(p, vs[jj][sub + 4 * i], acc[i]);
+    }
+    m = m_new;
+  }
+  if (row_valid) {
+    T* o = (T*)a.out + (size_t)(si.q_start + qi) * a.out_row_stride + (size_t)head * D;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) o[sub + 4 * i] = Num<T>::from_float(acc[i] * inv);
+  }
+}
+
+// ============================================================================ prefill, tensor cores
+constexpr int MMA_QT = 64, MMA_KT = 64;
+constexpr bool kHasMma = (D <= 128);
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(addr), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+#if LSE_HEAD_DIM <= 128
+__global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, int page_shift) {
+  constexpr int QT = MMA_QT, KT = MMA_KT, LD = D + 8, NCHUNK = D / 8, KS = D / 16, NB = KT / 8,
+                DB = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [QT][LD]
+  bf16* ks = qs + QT * LD;                       // [KT][LD]
+  bf16* vs = ks + KT * LD;                       // [KT][LD]
+  const int seq = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
+  const int head = blockIdx.y;
+  const int kvh = head / (a.num_heads / a.num_kv_heads);
+  const SeqInfo si = seq_info(a, seq);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
+  const int rows_here = min(QT, si.q_len - q0);
+  const int k_end = si.pos0 + q0 + rows_here;
+  const int k_first = a.window > 0 ? max(0, si.pos0 + q0 - a.window + 1) : 0;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const bf16* kp = (const bf16*)a.k_pages;
+  const bf16* vp = (const bf16*)a.v_pages;
+
+  // queries of this tile -> shared memory (rows past the portion are zero)
+  for (int idx = threadIdx.x; idx < QT * NCHUNK; idx += blockDim.x) {
+    const int r = idx / NCHUNK, c = idx - r * NCHUNK;
+    const bool ok = r < rows_here;
+    const bf16* src = (const bf16*)a.q + (size_t)(si.q_start + q0 + (ok ? r : 0)) * a.q_row_stride +
+                      (size_t)head * D + c * 8;
+    cp_async16(qs + r * LD + c * 8, src, ok);
+  }
+  asm volatile("cp.async.commit_group;\n" ::);
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  __syncthreads();
+  uint32_t qf[KS][4];
+#pragma unroll
+  for (int kk = 0; kk < KS; ++kk)
+    ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + ((lane >> 4) << 3));
+
+  float o[DB][4];
+#pragma unroll
+  for (int i = 0; i < DB; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+  const float sl2 = a.scale * 1.4426950408889634f;  // scores in the base-2 domain
+  const int qpos_r[2] = {si.pos0 + q0 + warp * 16 + g, si.pos0 + q0 + warp * 16 + g + 8};
+  const bool valid_r[2] = {warp * 16 + g < rows_here, warp * 16 + g + 8 < rows_here};
+
+  for (int k0 = (k_first / KT) * KT; k0 < k_end; k0 += KT) {
+    __syncthreads();  // everyone is done with the previous tile
+    for (int idx = threadIdx.x; idx < KT * NCHUNK; idx += blockDim.x) {
+      const int jj = idx / NCHUNK, c = idx - jj * NCHUNK;
+      const int j = k0 + jj;
+      const bool ok = j >= k_first && j < k_end;
+      size_t base = 0;
+      if (ok) {
+        int pi, off;
+        page_of(j, a.page_tokens, page_shift, pi, off);
+        base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D + c * 8;
+      }
+      cp_async16(ks + jj * LD + c * 8, kp + base, ok);
+      cp_async16(vs + jj * LD + c * 8, vp + base, ok);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncthreads();
+
+    // S = Q K^T for 16 rows x 64 keys
+    float s[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+      for (int nb = 0; nb < NB; nb += 2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, ks + (nb * 8 + (lane & 7) + ((lane >> 4) << 3)) * LD + kk * 16 +
+                           (((lane >> 3) & 1) << 3));
+        mma_bf16(s[nb], qf[kk], b[0], b[1]);
+        mma_bf16(s[nb + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    // mask, running maximum
+    float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int rr = e >> 1;
+        const int j = k0 + nb * 8 + t4 * 2 + (e & 1);
+        const bool ok = valid_r[rr] && j <= qpos_r[rr] && j >= k_first &&
+                        (a.window <= 0 || j > qpos_r[rr] - a.window);
+        s[nb][e] = ok ? s[nb][e] * sl2 : -INFINITY;
+        tmax[rr] = fmaxf(tmax[rr], s[nb][e]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
+      tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
+      const float m_new = fmaxf(m_r[rr], tmax[rr]);
+      m_use[rr] = (m_new == -INFINITY) ? 0.f : m_new;  // keeps exp2f(-inf - m_use) = 0, not NaN
+      corr[rr] = exp2f(m_r[rr] - m_use[rr]);
+      m_r[rr] = m_new;
+      l_r[rr] *= corr[rr];
+    }
+#pragma unroll
+    for (int i = 0; i < DB; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    // P = exp2(S - m), O += P V
+#pragma unroll
+    for (int kb = 0; kb < KT / 16; ++kb) {
+      uint32_t pa[4];
+      float p[2][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[h][e] = exp2f(s[2 * kb + h][e] - m_use[e >> 1]);
+          l_r[e >> 1] += p[h][e];
+        }
+      pa[0] = pack_bf16(p[0][0], p[0][1]);
+      pa[1] = pack_bf16(p[0][2], p[0][3]);
+      pa[2] = pack_bf16(p[1][0], p[1][1]);
+      pa[3] = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+      for (int db = 0; db < DB; db += 2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vs + (kb * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * LD + db * 8 +
+                                 ((lane >> 4) << 3));
+        mma_bf16(o[db], pa, b[0], b[1]);
+        mma_bf16(o[db + 1], pa, b[2], b[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    l_r[rr] += __shfl_xor_sync(0xffffffffu, l_r[rr], 1);
+    l_r[rr] += __shfl_xor_sync(0xffffffffu, l_r[rr], 2);
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    if (!valid_r[rr]) continue;
+    const float inv = l_r[rr] > 0.f ? 1.f / l_r[rr] : 0.f;
+    bf16* dst = (bf16*)a.out +
+                (size_t)(si.q_start + q0 + warp * 16 + g + rr * 8) * a.out_row_stride +
+                (size_t)head * D + t4 * 2;
+#pragma unroll
+    for (int db = 0; db < DB; ++db)
+      *reinterpret_cast<uint32_t*>(dst + db * 8) =
+          pack_bf16(o[db][rr * 2] * inv, o[db][rr * 2 + 1] * inv);
+  }
+}
+
+#endif  // LSE_HEAD_DIM <= 128
+
+// ============================================================================ decode
+// Lanes of a warp are arranged as (keys in flight) x (16-byte chunks of a row).
+template <typename T>
+struct DecodeShape {
+  static constexpr int VEC = Num<T>::kVec;
+  static constexpr int NCHUNK = D / VEC;
+  static constexpr int LPK = pow2_ceil(NCHUNK) < 32 ? pow2_ceil(NCHUNK) : 32;  // lanes per key
+  static constexpr int CPL = (NCHUNK + LPK - 1) / LPK;                          // chunks per lane
+  static constexpr int KPI = 32 / LPK;                                          // keys per warp pass
+};
+
+constexpr int DEC_WARPS = 4;
+
+template <typename T, int GT>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_split_kernel(const LseAttnArgs a, int page_shift) {
+  using S = DecodeShape<T>;
+  constexpr int VEC = S::VEC, NCHUNK = S::NCHUNK, LPK = S::LPK, CPL = S::CPL, KPI = S::KPI;
+  __shared__ float sm_m[DEC_WARPS][GT], sm_l[DEC_WARPS][GT];
+  __shared__ float sm_acc[DEC_WARPS][GT][D];
+
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int G = a.num_heads / a.num_kv_heads;
+  const int subs = (G + GT - 1) / GT;
+  const int kvh = blockIdx.y / subs, sub = blockIdx.y - kvh * subs;
+  const int h0 = kvh * G + sub * GT;
+  const int heads_here = min(GT, G - sub * GT);
+  const int seq = a.decode_seqs[b];
+  const int tok = a.cu_q[seq];
+  const int ctx = a.ctx_lens[seq];
+  const int k_first = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int span = ctx - k_first;
+  const int per = (span + a.num_splits - 1) / a.num_splits;
+  const int lo = k_first + split * per;
+  const int hi = min(ctx, lo + per);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int li = lane % LPK, slot = lane / LPK;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const T* kp = (const T*)a.k_pages;
+  const T* vp = (const T*)a.v_pages;
+
+  float qreg[GT][CPL][VEC], acc[GT][CPL][VEC], m[GT], l[GT];
+#pragma unroll
+  for (int gq = 0; gq < GT; ++gq) {
+    m[gq] = -INFINITY;
+    l[gq] = 0.f;
+    const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + min(gq, heads_here - 1)) * D;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) {
+      const int ch = li + c * LPK;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        qreg[gq][c][e] = ch < NCHUNK ? Num<T>::to_float(q[ch * VEC + e]) * a.scale : 0.f;
+        acc[gq][c][e] = 0.f;
+      }
+    }
+  }
+
+  for (int j0 = lo + warp * KPI; j0 < hi; j0 += DEC_WARPS * KPI) {
+    const int j = j0 + slot;
+    const bool ok = j < hi;
+    size_t base = 0;
+    if (ok) {
+      int pi, off;
+      page_of(j, a.page_tokens, page_shift, pi, off);
+      base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
+    }
+    Vec16<T> kv[CPL], vv[CPL];
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) {
+      const int ch = li + c * LPK;
+      if (ok && ch < NCHUNK) {
+        kv[c] = load16(kp + base + ch * VEC);
+        vv[c] = load16(vp + base + ch * VEC);
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) kv[c].v[e] = vv[c].v[e] = Num<T>::from_float(0.f);
+      }
+    }
+#pragma unroll
+    for (int gq = 0; gq < GT; ++gq) {
+      float d = 0.f;
+#pragma unroll
+      for (int c = 0; c < CPL; ++c)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) d = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[c].v[e]), d);
+#pragma unroll
+      for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      if (ok) {  // uniform over the LPK lanes of a key
+        const float m_new = fmaxf(m[gq], d);
+        const float corr = Exp<T>::f(m[gq] - m_new);
+        const float p = Exp<T>::f(d - m_new);
+        l[gq] = l[gq] * corr + p;
+#pragma unroll
+        for (int c = 0; c < CPL; ++c)
+#pragma unroll
+          for (int e = 0; e < VEC; ++e)
+            acc[gq][c][e] = fmaf(p, Num<T>::to_float(vv[c].v[e]), acc[gq][c][e] * corr);
+        m[gq] = m_new;
+      }
+    }
+  }
+
+  // merge the key slots of a warp (lanes that differ in the bits above LPK)
+#pragma unroll
+  for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+    for (int gq = 0; gq < GT; ++gq) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m[gq], o);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l[gq], o);
+      const float m_new = fmaxf(m[gq], m_o);
+      const float wa = (m[gq] == -INFINITY) ? 0.f : Exp<T>::f(m[gq] - m_new);
+      const float wb = (m_o == -INFINITY) ? 0.f : Exp<T>::f(m_o - m_new);
+      l[gq] = l[gq] * wa + l_o * wb;
+#pragma unroll
+      for (int c = 0; c < CPL; ++c)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          const float a_o = __shfl_xor_sync(0xffffffffu, acc[gq][c][e], o);
+          acc[gq][c][e] = acc[gq][c][e] * wa + a_o * wb;
+        }
+      m[gq] = m_new;
+    }
+  }
+  if (slot == 0) {
+#pragma unroll
+    for (int gq = 0; gq < GT; ++gq) {
+      if (li == 0) {
+        sm_m[warp][gq] = m[gq];
+        sm_l[warp][gq] = l[gq];
+      }
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) {
+        const int ch = li + c * LPK;
+        if (ch < NCHUNK)
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) sm_acc[warp][gq][ch * VEC + e] = acc[gq][c][e];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps; one thread per (head, dim)
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += blockDim.x) {
+    const int gq = idx / D, d = idx - gq * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][gq]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wt = (sm_m[w][gq] == -INFINITY) ? 0.f : Exp<T>::f(sm_m[w][gq] - M);
+      L += sm_l[w][gq] * wt;
+      A += sm_acc[w][gq][d] * wt;
+    }
+    const int h = h0 + gq;
+    if (a.num_splits == 1) {
+      T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+      o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+    } else {
+      float* part = a.scratch + (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
+      part[d] = A;
+      if (d == 0) {
+        part[D] = M;
+        part[D + 1] = L;
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void decode_merge_kernel(const LseAttnArgs a) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int seq = a.decode_seqs[b];
+  const int tok = a.cu_q[seq];
+  const float* part = a.scratch + ((size_t)b * a.num_heads + h) * a.num_splits * (D + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < a.num_splits; ++s) M = fmaxf(M, part[s * (D + 2) + D]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float L = 0.f, A = 0.f;
+    for (int s = 0; s < a.num_splits; ++s) {
+      const float ms = part[s * (D + 2) + D];
+      const float wt = (ms == -INFINITY) ? 0.f : Exp<T>::f(ms - M);
+      L += part[s * (D + 2) + D + 1] * wt;
+      A += part[s * (D + 2) + d] * wt;
+    }
+    T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+    o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+  }
+}
+
+static int shift_of(int n) {
+  if (n <= 0 || (n & (n - 1))) return -1;
+  int s = 0;
+  while ((1 << s) < n) ++s;
+  return s;
+}
+
+static bool args_ok(const LseAttnArgs* a) {
+  return a && (a->dtype == LSE_F32 || a->dtype == LSE_BF16) && a->num_heads > 0 &&
+         a->num_kv_heads > 0 && a->num_heads % a->num_kv_heads == 0 && a->page_tokens > 0 &&
+         a->window >= 0 && a->q && a->out && a->k_pages && a->v_pages && a->block_tables &&
+         a->ctx_lens && a->cu_q;
+}
+
+template <typename T>
+static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
+  const int G = a->num_heads / a->num_kv_heads;
+  const int ps = shift_of(a->page_tokens);
+  const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
+  dim3 grid(a->num_splits, a->num_kv_heads * ((G + gt - 1) / gt), a->num_decode);
+  if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
+  if (gt == 1) decode_split_kernel<T, 1><<<grid, DEC_WARPS * 32, 0, stream>>>(*a, ps);
+  else if (gt == 2) decode_split_kernel<T, 2><<<grid, DEC_WARPS * 32, 0, stream>>>(*a, ps);
+  else decode_split_kernel<T, 4><<<grid, DEC_WARPS * 32, 0, stream>>>(*a, ps);
+  if (cudaGetLastError() != cudaSuccess) return LSE_LAUNCH_FAILED;
+  if (a->num_splits > 1) {
+    dim3 mgrid(a->num_decode, a->num_heads);
+    decode_merge_kernel<T><<<mgrid, D < 32 ? 32 : (D > 128 ? 128 : D), 0, stream>>>(*a);
+    if (cudaGetLastError() != cudaSuccess) return LSE_LAUNCH_FAILED;
+  }
+  return LSE_OK;
+}
+
+}  // namespace lse
+
+using namespace lse;
+
+extern "C" int lse_attn_head_dim(void) { return D; }
+
+extern "C" int lse_attn_q_tile(int dtype) {
+  return (dtype == LSE_BF16 && kHasMma) ? MMA_QT : SIMT_QT;
+}
+
+extern "C" size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, int num_splits) {
+  return num_splits > 1 ? (size_t)num_decode * num_heads * num_splits * (D + 2) : 0;
+}
+
+extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
+  if (!args_ok(a) || (a->num_tiles > 0 && !a->tiles)) return LSE_BAD_ARGUMENT;
+  if (a->num_tiles <= 0) return LSE_OK;
+  if (a->num_heads > 65535) return LSE_BAD_ARGUMENT;
+  const int ps = shift_of(a->page_tokens);
+  dim3 grid(a->num_tiles, a->num_heads);
+  if (a->dtype == LSE_F32) {
+    prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
+  } else if (!kHasMma || a->force_simt) {
+    // the caller built tiles of SIMT_QT rows in this case
+    prefill_simt_kernel<bf16><<<grid, 128, 0, stream>>>(*a, ps);
+  } else {
+#if LSE_HEAD_DIM <= 128
+    constexpr int smem = (MMA_QT + 2 * MMA_KT) * (D + 8) * (int)sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               smem) != cudaSuccess)
+        return LSE_LAUNCH_FAILED;
+      configured = true;
+    }
+    prefill_mma_kernel<<<grid, 128, smem, stream>>>(*a, ps);
+#endif
+  }
+  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+}
+
+extern "C" int lse_attn_decode(const LseAttnArgs* a, cudaStream_t stream) {
+  if (!args_ok(a) || (a->num_decode > 0 && !a->decode_seqs)) return LSE_BAD_ARGUMENT;
+  if (a->num_decode <= 0) return LSE_OK;
+  if (a->num_splits < 1 || (a->num_splits > 1 && !a->scratch)) return LSE_BAD_ARGUMENT;
+  return a->dtype == LSE_F32 ? launch_decode<float>(a, stream) : launch_decode<bf16>(a, stream);
+}

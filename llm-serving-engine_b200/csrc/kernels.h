@@ -1,0 +1,65 @@
+// C launch interface of the engine's CUDA kernels. Every function enqueues work on `stream` and
+// returns LSE_OK, or a non-zero code with nothing enqueued when an argument cannot be served.
+// dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "status.h"
+
+#define LSE_F32 0
+#define LSE_BF16 1
+
+extern "C" {
+
+// out[t, :] = float(table[ids[t], :])                      out float32 [T, H]
+int lse_embedding(const int* ids, const void* table, int table_dtype, float* out, int T, int H,
+                  cudaStream_t stream);
+
+// Residual add and RMS norm.
+//   rows == nullptr: for every row t < T: if residual: x[t] += residual[t] (in place, float32);
+//                    out[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * weight
+//   rows != nullptr: out[r] = norm(x[rows[r]] (+ residual[rows[r]])) for r < T; x is not written.
+int lse_add_rmsnorm(float* x, const void* residual, int residual_dtype, const float* weight,
+                    float eps, void* out, int out_dtype, const int* rows, int T, int H,
+                    cudaStream_t stream);
+
+// Rotate q and k heads of the fused projection in place (q only is kept there) and write this
+// step's k and v rows into their pages.
+//   qkv [T, (nq + 2 nk) D]; cos/sin float32 [max_pos, D/2] or nullptr for no rotation;
+//   k_pages/v_pages [pages, nk, page_tokens, D] or nullptr when this layer only reads a cache.
+int lse_rope_kv_write(void* qkv, int dtype, int T, int nq, int nk, int D, const int* positions,
+                      const int* token_seq, const float* cos, const float* sin, void* k_pages,
+                      void* v_pages, const int* block_tables, int table_stride, int page_tokens,
+                      cudaStream_t stream);
+
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]               gu [T, 2I], out [T, I]
+int lse_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream);
+
+// True float32 matrix product: out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]). Each output element is
+// accumulated over k in ascending order by one thread, so a row's result does not depend on T.
+int lse_gemm_f32(const float* a, const float* w, const float* bias, float* out, int T, int N, int K,
+                 cudaStream_t stream);
+
+// Sampling. One token per row of logits [R, V] (float32, row stride V).
+//   temperature[r] < 1e-5 selects the largest logit (lowest index on ties). Otherwise the row is
+//   divided by its temperature, cut to top_k / top_p / min_p, and a token is drawn by the
+//   exponential race: argmax p_i / E_i, E_i ~ Exp(1) from a counter-based generator keyed by
+//   (seed[r], draw[r], i).
+int lse_sample(const float* logits, int R, int V, const float* temperature, const int* top_k,
+               const float* top_p, const float* min_p, const uint64_t* seed, const int* draw,
+               int* out_tokens, cudaStream_t stream);
+
+// out[r] = log(sum_i exp(logits[r, i]))
+int lse_logsumexp(const float* logits, int R, int V, float* out, cudaStream_t stream);
+
+// logits[row, token] += / *= per the penalties; entries are unique (row, token) pairs.
+int lse_apply_penalties(float* logits, int V, const int* row, const int* token, const int* count,
+                        const float* presence, const float* frequency, const float* repetition,
+                        int n, cudaStream_t stream);
+
+// logits[row[i], token[i]] = -inf
+int lse_ban_tokens(float* logits, int V, const int* row, const int* token, int n,
+                   cudaStream_t stream);
+}

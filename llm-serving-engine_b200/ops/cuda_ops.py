@@ -1,0 +1,178 @@
+"""The kernel set of the product path: thin, checked calls into the sm_100a extension.
+
+There is no other implementation behind these methods: if CUDA or the compiled extension is not
+available, constructing :class:`CudaOps` raises.
+
+Matrix products: float32 runs this package's own CUDA-core kernel (true 32-bit, no tensor-core
+mode). bfloat16 products go to cuBLAS through ``torch.mm`` with float32 accumulation, the same
+library-for-linear-layers split as the reference (src/llmserve/models/layers.py:129-152).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import build
+
+_DTYPES = (torch.float32, torch.bfloat16)
+
+
+class CudaOps:
+    name = "cuda-sm100a"
+
+    def __init__(self, device: torch.device | str = "cuda") -> None:
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise RuntimeError(
+                "llmserve_b200 runs on a CUDA device only (built for sm_100a); no CPU fallback exists"
+            )
+        self.ext = build.load_core()
+        self._attn_loaded: set[int] = set()
+        self._scratch: torch.Tensor | None = None
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.force_simt_attention = False
+        self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
+
+    # ------------------------------------------------------------------ capabilities
+    def branch_dtype(self, dtype: torch.dtype) -> torch.dtype:
+        """Dtype in which projections that feed the residual stream return their result."""
+        return torch.float32
+
+    def check_attention_shape(self, head_dim: int, dtype: torch.dtype) -> None:
+        if dtype not in _DTYPES:
+            raise ValueError(f"attention kernels exist for float32 and bfloat16, not {dtype}")
+        if head_dim not in self._attn_loaded:
+            self.ext.load_attention_library(build.attention_library(head_dim), head_dim)
+            self._attn_loaded.add(head_dim)
+
+    # ------------------------------------------------------------------ pointwise
+    def embedding(self, token_ids, table):
+        out = torch.empty(token_ids.shape[0], table.shape[1], dtype=torch.float32, device=table.device)
+        self.ext.embedding(token_ids, table, out)
+        self.launches += 1
+        return out
+
+    def add_rmsnorm(self, x, residual, weight, eps, out_dtype, rows=None):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
+        self.ext.add_rmsnorm(x, residual, weight, float(eps), out, rows)
+        self.launches += 1
+        return out
+
+    def silu_mul(self, gu):
+        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
+        self.ext.silu_mul(gu, out)
+        self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ matrix products
+    def linear(self, a, w, bias=None, out_dtype=None):
+        out_dtype = out_dtype or a.dtype
+        if a.dtype == torch.float32:
+            if w.dtype != torch.float32:
+                raise TypeError("float32 activations need float32 weights")
+            out = torch.empty(a.shape[0], w.shape[0], dtype=torch.float32, device=a.device)
+            self.ext.gemm_f32(a, w, bias, out)
+            self.launches += 1
+            return out if out_dtype == torch.float32 else out.to(out_dtype)
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            raise TypeError(f"linear: unsupported dtypes {a.dtype} x {w.dtype}")
+        if out_dtype == torch.float32:
+            out = torch.mm(a, w.t(), out_dtype=torch.float32)
+            if bias is not None:
+                out += bias.float()
+            return out
+        out = torch.mm(a, w.t())
+        if bias is not None:
+            out += bias
+        return out
+
+    # ------------------------------------------------------------------ attention
+    def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
+                      cos, sin, k_pages, v_pages, block_tables, page_tokens):
+        self.ext.rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, positions, token_seq,
+                               cos, sin, k_pages, v_pages, block_tables, page_tokens)
+        self.launches += 1
+
+    def attention_q_tile(self, dtype, head_dim):
+        return int(self.ext.attention_q_tile(head_dim, dtype == torch.bfloat16,
+                                             self.force_simt_attention))
+
+    def attention_plan(self, host_step, dtype, head_dim):
+        """Work lists for this step: tiles of the portions, and the single-token sequences."""
+        qt = self.attention_q_tile(dtype, head_dim)
+        tiles, decode = [], []
+        for s, n in enumerate(host_step.q_lens.tolist()):
+            if n == 1:
+                decode.append(s)
+            else:
+                tiles.extend((s, q0) for q0 in range(0, n, qt))
+        # longest contexts first: their tiles run longest
+        tiles.sort(key=lambda t: -(int(host_step.ctx_lens[t[0]]) - int(host_step.q_lens[t[0]]) + t[1]))
+        return {
+            "tiles": np.asarray(tiles, dtype=np.int32).reshape(-1, 2),
+            "decode_seqs": np.asarray(decode, dtype=np.int32),
+        }
+
+    def decode_splits(self, num_decode, num_kv_heads, max_ctx):
+        """Context partitions per (sequence, head) so that the grid fills the GPU about twice."""
+        if num_decode == 0:
+            return 1
+        blocks = num_decode * num_kv_heads
+        want = max(1, (2 * self.num_sms + blocks - 1) // blocks)
+        return int(max(1, min(want, (max_ctx + 255) // 256, 64)))
+
+    def paged_attention(self, qkv, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
+                        v_pages, block_tables, page_tokens, step, plan):
+        out = torch.empty(qkv.shape[0], num_heads * head_dim, dtype=qkv.dtype, device=qkv.device)
+        n_tiles = int(plan["tiles"].shape[0])
+        n_dec = int(plan["decode_seqs"].shape[0])
+        splits = step.decode_splits if step.decode_splits else self.decode_splits(
+            n_dec, num_kv_heads, step.max_decode_ctx)
+        scratch = None
+        if n_dec and splits > 1:
+            need = int(self.ext.attention_scratch_floats(head_dim, n_dec, num_heads, splits))
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+            scratch = self._scratch
+        self.ext.paged_attention(
+            qkv, out, k_pages, v_pages, num_heads, num_kv_heads, head_dim, float(scale),
+            int(window), block_tables, step.ctx_lens, step.cu_q,
+            plan["tiles"] if n_tiles else None, n_tiles,
+            plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,
+            self.force_simt_attention,
+        )
+        self.launches += (1 if n_tiles else 0) + (0 if not n_dec else (2 if splits > 1 else 1))
+        return out
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw):
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        self.ext.sample(logits, temperature, top_k, top_p, min_p, seed, draw, out)
+        self.launches += 1
+        return out
+
+    def logsumexp(self, logits):
+        out = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+        self.ext.logsumexp(logits, out)
+        self.launches += 1
+        return out
+
+    def apply_penalties(self, logits, row, token, count, presence, frequency, repetition):
+        self.ext.apply_penalties(logits, row, token, count, presence, frequency, repetition)
+        self.launches += 1
+
+    def ban_tokens(self, logits, row, token):
+        self.ext.ban_tokens(logits, row, token)
+        self.launches += 1
+
+
+_instances: dict[str, CudaOps] = {}
+
+
+def get_ops(device: torch.device | str = "cuda") -> CudaOps:
+    key = str(torch.device(device))
+    if key not in _instances:
+        _instances[key] = CudaOps(device)
+    return _instances[key]

@@ -1,0 +1,227 @@
+"""Each CUDA kernel alone against its plain PyTorch version, at sizes the engine's models do not use."""
+
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from plain_ops import PlainOps
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llmserve_b200.ops import get_ops
+
+    return get_ops("cuda")
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(a, b, dtype, atol32=1e-5, rel16=0.01):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs().max().item()
+    bound = atol32 * max(1.0, b.abs().max().item()) if dtype == "float32" else rel16 * b.abs().max().item()
+    assert err <= bound, f"max error {err:.3e} > {bound:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,H,V", [(1, 24, 37), (7, 100, 50), (33, 2048, 300)])
+def test_embedding(ops, dtype, T, H, V):
+    table = rnd(V, H, dtype=DT[dtype])
+    ids = torch.randint(0, V, (T,), dtype=torch.int32)
+    got = ops.embedding(ids.cuda(), table.cuda())
+    assert got.dtype == torch.float32
+    assert torch.equal(got.cpu(), PlainOps().embedding(ids, table))
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("res_dtype", [None, "float32", "bfloat16"])
+@pytest.mark.parametrize("T,H", [(1, 40), (5, 1000), (19, 4100)])
+def test_add_rmsnorm(ops, out_dtype, res_dtype, T, H):
+    x = rnd(T, H, seed=1, scale=3.0)
+    r = None if res_dtype is None else rnd(T, H, dtype=DT[res_dtype], seed=2)
+    w = 1 + rnd(H, seed=3, scale=0.1)
+    xg = x.clone().cuda()
+    got = ops.add_rmsnorm(xg, None if r is None else r.cuda(), w.cuda(), 1e-5, DT[out_dtype])
+    xr = x.clone()
+    ref = PlainOps().add_rmsnorm(xr, r, w, 1e-5, DT[out_dtype])
+    assert torch.allclose(xg.cpu(), xr, atol=1e-6), "residual stream"
+    close(got, ref, out_dtype, atol32=2e-6, rel16=0.005)
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32)
+    xg2 = x.clone().cuda()
+    got = ops.add_rmsnorm(xg2, None if r is None else r.cuda(), w.cuda(), 1e-5, DT[out_dtype], rows=rows.cuda())
+    ref = PlainOps().add_rmsnorm(x.clone(), r, w, 1e-5, DT[out_dtype], rows=rows)
+    assert torch.equal(xg2.cpu(), x), "rows mode must not write x"
+    close(got, ref, out_dtype, atol32=2e-6, rel16=0.005)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,I", [(1, 7), (3, 160), (40, 2744)])
+def test_silu_mul(ops, dtype, T, I):
+    gu = rnd(T, 2 * I, dtype=DT[dtype], scale=2.0)
+    close(ops.silu_mul(gu.cuda()), PlainOps().silu_mul(gu), dtype, atol32=1e-6, rel16=0.005)
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 5, 3), (3, 130, 70), (65, 64, 257), (130, 1000, 96)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_f32_is_true_float32_and_batch_invariant(ops, T, N, K, bias):
+    a, w = rnd(T, K, seed=1), rnd(N, K, seed=2)
+    b = rnd(N, seed=3) if bias else None
+    got = ops.linear(a.cuda(), w.cuda(), None if b is None else b.cuda(), out_dtype=torch.float32).cpu()
+    ref = a.double() @ w.double().T + (0 if b is None else b.double())
+    assert (got.double() - ref).abs().max() < 2e-6 * K**0.5 * 4
+    # the same row gives the same bits whatever else is in the batch
+    alone = ops.linear(a[T // 2 : T // 2 + 1].cuda(), w.cuda(), None if b is None else b.cuda(),
+                       out_dtype=torch.float32).cpu()
+    assert torch.equal(alone[0], got[T // 2])
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16"])
+@pytest.mark.parametrize("T,N,K", [(1, 48, 64), (9, 520, 200), (300, 136, 1000)])
+def test_linear_bf16(ops, dtype, T, N, K):
+    a, w = rnd(T, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    for od in (torch.bfloat16, torch.float32):
+        got = ops.linear(a.cuda(), w.cuda(), None, out_dtype=od)
+        assert got.dtype == od
+        close(got, a.float() @ w.float().T, "bfloat16", rel16=0.006)
+
+
+def paged_case(nseq, q_lens, ctx_lens, nq, nk, D, page, dtype, seed=0, shuffle=True):
+    """Random q/k/v rows, a cache whose pages are handed out in shuffled order."""
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-c // page) for c in ctx_lens]
+    num_pages = sum(blocks) + 3
+    order = torch.randperm(num_pages, generator=g).tolist() if shuffle else list(range(num_pages))
+    width = max(blocks)
+    tables = torch.zeros(nseq, width, dtype=torch.int32)
+    it = iter(order)
+    for s in range(nseq):
+        for b in range(blocks[s]):
+            tables[s, b] = next(it)
+    T = sum(q_lens)
+    qkv = (torch.randn(T, (nq + 2 * nk) * D, generator=g)).to(dtype)
+    # stale contents everywhere: huge values that would wreck the result if ever read
+    k_pages = torch.full((num_pages, nk, page, D), 300.0).to(dtype)
+    v_pages = torch.full((num_pages, nk, page, D), -7e4 if dtype == torch.float32 else -3e4).to(dtype)
+    cu = np.zeros(nseq + 1, dtype=np.int32)
+    cu[1:] = np.cumsum(q_lens)
+    # fill the cached part (positions before this step's tokens) with random rows
+    for s in range(nseq):
+        for p in range(ctx_lens[s] - q_lens[s]):
+            pg, off = int(tables[s, p // page]), p % page
+            k_pages[pg, :, off] = torch.randn(nk, D, generator=g).to(dtype)
+            v_pages[pg, :, off] = torch.randn(nk, D, generator=g).to(dtype)
+    positions = torch.cat([torch.arange(c - q, c) for q, c in zip(q_lens, ctx_lens)]).int()
+    token_seq = torch.cat([torch.full((q,), s) for s, q in enumerate(q_lens)]).int()
+    step = SimpleNamespace(cu_q=torch.from_numpy(cu), ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32),
+                           q_lens=np.asarray(q_lens, dtype=np.int32), decode_splits=0,
+                           max_decode_ctx=max([c for q, c in zip(q_lens, ctx_lens) if q == 1] or [0]))
+    return qkv, k_pages, v_pages, tables, positions, token_seq, step
+
+
+def run_attention(ops, case, nq, nk, D, page, window, max_pos, theta=10000.0, splits=0, rope=True):
+    qkv, kp, vp, tables, positions, token_seq, step = case
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), inv)
+    cos, sin = (ang.cos().float(), ang.sin().float()) if rope else (None, None)
+    scale = D**-0.5
+    plain = PlainOps()
+    q_ref, kp_ref, vp_ref = qkv.clone(), kp.clone(), vp.clone()
+    kw = dict(num_heads=nq, num_kv_heads=nk, head_dim=D)
+    plain.rope_kv_write(q_ref, **kw, positions=positions, token_seq=token_seq, cos=cos, sin=sin,
+                        k_pages=kp_ref, v_pages=vp_ref, block_tables=tables, page_tokens=page)
+    ref = plain.paged_attention(q_ref, **kw, scale=scale, window=window, k_pages=kp_ref,
+                                v_pages=vp_ref, block_tables=tables, page_tokens=page, step=step)
+    dev = lambda t: None if t is None else t.cuda()
+    ops.check_attention_shape(D, qkv.dtype)
+    q_g, kp_g, vp_g = qkv.cuda(), kp.cuda(), vp.cuda()
+    ops.rope_kv_write(q_g, **kw, positions=dev(positions), token_seq=dev(token_seq), cos=dev(cos),
+                      sin=dev(sin), k_pages=kp_g, v_pages=vp_g, block_tables=dev(tables), page_tokens=page)
+    gstep = SimpleNamespace(cu_q=step.cu_q.cuda(), ctx_lens=step.ctx_lens.cuda(), decode_splits=splits,
+                            max_decode_ctx=step.max_decode_ctx)
+    plan = {k: torch.from_numpy(v).cuda() for k, v in ops.attention_plan(step, qkv.dtype, D).items()}
+    got = ops.paged_attention(q_g, **kw, scale=scale, window=window, k_pages=kp_g, v_pages=vp_g,
+                              block_tables=dev(tables), page_tokens=page, step=gstep, plan=plan)
+    return got, ref, (q_g, q_ref, kp_g, kp_ref, vp_g, vp_ref)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nk,D,page", [(4, 4, 64, 16), (6, 2, 48, 8), (8, 1, 128, 32), (5, 5, 16, 4), (3, 1, 80, 7)])
+def test_rope_kv_write_and_attention_mixed_batch(ops, dtype, nq, nk, D, page):
+    q_lens = [1, 70, 1, 2, 130, 1]
+    ctx_lens = [1, 70, 513, 40, 300, 65]
+    case = paged_case(6, q_lens, ctx_lens, nq, nk, D, page, DT[dtype], seed=4)
+    got, ref, (q_g, q_ref, kp_g, kp_ref, vp_g, vp_ref) = run_attention(ops, case, nq, nk, D, page, 0, 600)
+    close(q_g[:, : nq * D], q_ref[:, : nq * D], dtype, atol32=2e-6, rel16=0.005)
+    close(kp_g, kp_ref, dtype, atol32=2e-6, rel16=0.005)
+    assert torch.equal(vp_g.cpu(), vp_ref)
+    close(got, ref, dtype, atol32=1e-5, rel16=0.02)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_window_edges(ops, dtype, window):
+    q_lens, ctx_lens = [1, 97, 1, 3], [200, 150, 64, 66]
+    case = paged_case(4, q_lens, ctx_lens, 4, 2, 32, 16, DT[dtype], seed=6)
+    got, ref, _ = run_attention(ops, case, 4, 2, 32, 16, window, 256)
+    close(got, ref, dtype, atol32=1e-5, rel16=0.02)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("splits", [1, 3, 16])
+def test_decode_split_counts_agree(ops, dtype, splits):
+    q_lens, ctx_lens = [1, 1, 1], [1000, 17, 255]
+    case = paged_case(3, q_lens, ctx_lens, 6, 2, 64, 16, DT[dtype], seed=8)
+    got, ref, _ = run_attention(ops, case, 6, 2, 64, 16, 0, 1024, splits=splits)
+    close(got, ref, dtype, atol32=1e-5, rel16=0.02)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 15, 16, 700, 1023])
+def test_one_far_key_stands_out(ops, dtype, far):
+    """One key among a thousand is made to win the softmax; the output must be its value row."""
+    nq = nk = 2
+    D, page, ctx = 64, 16, 1024
+    for q_lens in ([1], [24]):
+        case = paged_case(1, q_lens, [ctx], nq, nk, D, page, DT[dtype], seed=far + 1)
+        qkv, kp, vp, tables, positions, token_seq, step = case
+        if far >= ctx - q_lens[0]:
+            continue  # the far key must lie in the cached part
+        qkv[-1, : nq * D] = 0
+        qkv[-1, 3] = 8.0
+        qkv[-1, D + 3] = 8.0  # both heads look along dimension 3
+        pg, off = int(tables[0, far // page]), far % page
+        kp[pg, :, off] = 0
+        kp[pg, :, off, 3] = 20.0
+        got, ref, _ = run_attention(ops, case, nq, nk, D, page, 0, ctx, rope=False)
+        want = vp[pg, :, off].float().reshape(-1)
+        assert (got[-1].float().cpu() - want).abs().max() < (1e-4 if dtype == "float32" else 0.02)
+        close(got, ref, dtype, atol32=1e-5, rel16=0.02)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16"])
+def test_tensor_core_and_cuda_core_prefill_agree(ops, dtype):
+    case = paged_case(2, [150, 64], [150, 200], 4, 2, 64, 16, torch.bfloat16, seed=3)
+    a, ref, _ = run_attention(ops, case, 4, 2, 64, 16, 0, 256)
+    ops.force_simt_attention = True
+    try:
+        b, _, _ = run_attention(ops, case, 4, 2, 64, 16, 0, 256)
+    finally:
+        ops.force_simt_attention = False
+    close(a, ref, dtype, rel16=0.02)
+    close(b, ref, dtype, rel16=0.02)
+
+
+def test_unsupported_head_size_is_refused(ops):
+    with pytest.raises(ValueError, match="head size"):
+        ops.check_attention_shape(40, torch.bfloat16)
+    with pytest.raises(ValueError, match="head size"):
+        ops.check_attention_shape(512, torch.float32)

@@ -65,6 +65,7 @@ class _Held:
     slot: int
     computed: int = 0
     tables: list[list[int]] = field(default_factory=list)  # one per group
+    epoch: int = 0  # number of the admission; a new holder of the same slot has another one
 
 
 class CacheManager:
@@ -78,6 +79,7 @@ class CacheManager:
         self.max_requests = max_requests
         self.free_slots: list[int] = list(range(max_requests - 1, -1, -1))
         self.held: dict[object, _Held] = {}
+        self._epochs = 0
 
     # ------------------------------------------------------------------ admission
     def is_live(self, rid) -> bool:
@@ -93,7 +95,8 @@ class CacheManager:
         if not self.free_slots:
             raise OutOfPages("no free state slot")
         slot = self.free_slots.pop()
-        self.held[rid] = _Held(slot, 0, [[] for _ in self.groups])
+        self._epochs += 1
+        self.held[rid] = _Held(slot, 0, [[] for _ in self.groups], self._epochs)
         return slot
 
     # ------------------------------------------------------------------ capacity
@@ -165,6 +168,9 @@ class CacheManager:
 
     def state_slot(self, rid) -> int:
         return self.held[rid].slot
+
+    def epoch(self, rid) -> int:
+        return self.held[rid].epoch
 
     def num_computed(self, rid) -> int:
         return self.held[rid].computed

@@ -1,0 +1,184 @@
+"""CUDA graphs for steps that hold single tokens only.
+
+A decode step at small batch is a few hundred short kernels; launching them one by one costs more
+than running them. Such a step (every entry one token, every entry sampled) is therefore captured
+once per (batch size, number of context partitions) as a CUDA graph over fixed device buffers and
+replayed: per step the host fills one pinned buffer (token ids, positions, context lengths, block
+tables, sampling parameters), copies it to the device in one transfer, replays the graph (model
+forward and sampling kernel) and reads the sampled token ids back.
+
+The graph runs the same model code, kernels and cache as an uncaptured step; only the launch
+mechanism differs.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from .batch import DeviceStep, StepEntry
+
+
+class _Graph:
+    def __init__(self, owner: "DecodeGraphs", batch: int, splits: int) -> None:
+        runner = owner.runner
+        self.batch = B = batch
+        dev = runner.device
+        widths = [-(-runner.max_model_len // g.page_tokens) for g in runner.manager.groups]
+        # layout of the per-step buffer, in int32 words
+        names = ["token_ids", "positions", "ctx_lens", "state_slots", "first_portion",
+                 "temperature", "top_k", "top_p", "min_p", "draw"]
+        self.off, n = {}, 0
+        for name in names:
+            self.off[name] = n
+            n += (B + 3) // 4 * 4
+        self.off["seed"] = n  # int64: two words each, at an even offset
+        n += 2 * ((B + 1) // 2 * 2)
+        self.table_off = []
+        for w in widths:
+            self.table_off.append((n, w))
+            n += B * w
+        self.words = n
+        self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        self.h = self.host.numpy()
+        self.dev = torch.zeros(n, dtype=torch.int32, device=dev)
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        view = lambda name: self.dev[self.off[name] : self.off[name] + B]
+        plans = {
+            key: {"tiles": torch.zeros(0, 2, dtype=torch.int32, device=dev), "decode_seqs": ar[:B]}
+            for key in runner.planners
+        }
+        self.step = DeviceStep(
+            token_ids=view("token_ids"), positions=view("positions"), token_seq=ar[:B], cu_q=ar,
+            ctx_lens=view("ctx_lens"), state_slots=view("state_slots"),
+            first_portion=view("first_portion"),
+            block_tables=[self.dev[o : o + B * w].view(B, w) for o, w in self.table_off],
+            logit_rows=ar[:B], num_tokens=B, num_seqs=B, num_logit_rows=B, max_decode_ctx=0,
+            decode_splits=splits, plans=plans, host=None,
+        )
+        f32 = lambda name: view(name).view(torch.float32)
+        so = self.off["seed"]
+        self.sample_args = (f32("temperature"), view("top_k"), f32("top_p"), f32("min_p"),
+                            self.dev[so : so + 2 * B].view(torch.int64), view("draw"))
+        self.tokens_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.tokens: torch.Tensor | None = None
+        self.launches = 0
+
+    def hview(self, name, dtype=np.int32):
+        B = self.batch
+        return self.h[self.off[name] : self.off[name] + B].view(dtype)
+
+
+class DecodeGraphs:
+    def __init__(self, runner) -> None:
+        self.runner = runner
+        self.graphs: dict[tuple[int, int], _Graph] = {}
+        self.pool = None
+        groups = runner.manager.groups
+        self.min_kv_heads = min((g.num_kv_heads for g in groups), default=1)
+        # host mirror of every live request's block tables, by state slot, grown page by page
+        self.mirror = [
+            np.zeros((runner.manager.max_requests, -(-runner.max_model_len // g.page_tokens)), np.int32)
+            for g in groups
+        ]
+        self.mirror_len = np.zeros((len(groups), runner.manager.max_requests), dtype=np.int64)
+        self.mirror_epoch = np.zeros(runner.manager.max_requests, dtype=np.int64)
+
+    @staticmethod
+    def usable(entries: Sequence[StepEntry], rows) -> bool:
+        if len(rows) != len(entries):
+            return False
+        for e in entries:
+            if len(e.tokens) != 1 or list(e.want) != [0]:
+                return False
+        for r in rows:
+            if r.params.has_penalties or r.banned_token_ids or r.params.logprobs is not None:
+                return False
+        return True
+
+    def _fill(self, g: _Graph, entries, rows) -> int:
+        m = self.runner.manager
+        B = g.batch
+        tok, pos, ctx = g.hview("token_ids"), g.hview("positions"), g.hview("ctx_lens")
+        slots, first = g.hview("state_slots"), g.hview("first_portion")
+        for i, e in enumerate(entries):
+            held = m.held[e.rid]
+            c = held.computed
+            tok[i] = e.tokens[0]
+            pos[i] = c
+            ctx[i] = c + 1
+            slots[i] = s = held.slot
+            first[i] = c == 0
+            if self.mirror_epoch[s] != held.epoch:
+                self.mirror_epoch[s] = held.epoch
+                self.mirror_len[:, s] = 0
+            for gi, table in enumerate(held.tables):
+                known = self.mirror_len[gi, s]
+                if len(table) > known:
+                    self.mirror[gi][s, known : len(table)] = np.maximum(table[known:], 0)
+                    self.mirror_len[gi, s] = len(table)
+                need = -(-(c + 1) // m.groups[gi].page_tokens)
+                if len(table) < need:
+                    raise ValueError(f"request {e.rid!r}: block table has {len(table)} pages, needs {need}")
+        if int(ctx.max()) > self.runner.max_model_len:
+            raise ValueError("a sequence would outgrow max_model_len")
+        v = self.runner.model.plan.vocab_size
+        if int(tok.min()) < 0 or int(tok.max()) >= v:
+            raise ValueError(f"token ids must lie in [0, {v})")
+        for gi, (o, w) in enumerate(g.table_off):
+            g.h[o : o + B * w].reshape(B, w)[:] = self.mirror[gi][slots]
+        p = [r.params for r in rows]
+        g.hview("temperature", np.float32)[:] = [q.temperature for q in p]
+        g.hview("top_k")[:] = [q.top_k for q in p]
+        g.hview("top_p", np.float32)[:] = [q.top_p for q in p]
+        g.hview("min_p", np.float32)[:] = [q.min_p for q in p]
+        g.hview("draw")[:] = [len(r.output_token_ids) for r in rows]
+        so = g.off["seed"]
+        g.h[so : so + 2 * B].view(np.uint64)[:] = [r.seed & 0xFFFFFFFFFFFFFFFF for r in rows]
+        return int(ctx.max())
+
+    def _forward(self, g: _Graph):
+        runner = self.runner
+        logits = runner.model.forward(g.step, runner.pools)
+        return runner.ops.sample(logits, *g.sample_args)
+
+    def _capture(self, g: _Graph) -> None:
+        ops = self.runner.ops
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            for _ in range(2):  # warm-up on the step's own data: the writes are idempotent
+                self._forward(g)
+        cur.wait_stream(side)
+        torch.cuda.synchronize()
+        before = ops.launches
+        g.graph = torch.cuda.CUDAGraph()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(g.graph, pool=self.pool):
+            g.tokens = self._forward(g)
+        g.launches = ops.launches - before
+
+    def run(self, entries: Sequence[StepEntry], rows) -> list[int]:
+        runner = self.runner
+        B = len(entries)
+        max_ctx = 1 + max(runner.manager.held[e.rid].computed for e in entries)
+        splits = runner.ops.decode_splits(B, self.min_kv_heads, max_ctx)
+        key = (B, splits)
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = _Graph(self, B, splits)
+        self._fill(g, entries, rows)
+        g.dev.copy_(g.host, non_blocking=True)
+        if g.graph is None:
+            self._capture(g)
+        g.graph.replay()
+        runner.ops.launches += g.launches
+        g.tokens_host.copy_(g.tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        runner.steps_run += 1
+        return g.tokens_host.tolist()

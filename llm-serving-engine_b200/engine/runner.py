@@ -90,6 +90,11 @@ class ModelRunner:
         self.manager = CacheManager(kv_groups, pages, max_num_seqs)
         self.pools = CachePools(kv_groups, state_groups, pages, max_num_seqs, self.dtype, self.device)
         self.planners = model.step_planners()
+        for mixer, _ in self.planners.values():
+            mixer.reserve(max_num_seqs)
+        self.decode_graphs = None
+        self.last_h2d_bytes = 0
+        self.last_d2h_bytes = 0
         self._staging: list[tuple[torch.Tensor, Any]] = []
         self._staging_turn = 0
         self.steps_run = 0
@@ -138,6 +143,7 @@ class ModelRunner:
         if self.device.type == "cuda":
             dev = torch.empty(total, dtype=torch.int32, device=self.device)
             dev.copy_(stage[:total], non_blocking=True)
+            self.last_h2d_bytes = 4 * total
             ev = torch.cuda.Event()
             ev.record()
             self._staging[idx] = (stage, ev)
@@ -185,3 +191,25 @@ class ModelRunner:
     def finish(self, rid) -> None:
         """Give back everything ``rid`` holds."""
         self.manager.release(rid)
+
+    def step_and_sample(self, entries: Sequence[StepEntry], sampler, rows, graphs: bool = False):
+        """A step followed by sampling on the device; only token ids come back to the host.
+
+        ``rows`` has one :class:`~llmserve_b200.sampling.SampleRow` per wanted place, in order.
+        """
+        if graphs and self.device.type == "cuda":
+            from ..sampling.sampler import SamplerOutput
+            from .decode_graph import DecodeGraphs
+
+            if DecodeGraphs.usable(entries, rows):
+                if self.decode_graphs is None:
+                    self.decode_graphs = DecodeGraphs(self)
+                tokens = self.decode_graphs.run(entries, rows)
+                g = self.decode_graphs
+                self.last_h2d_bytes = 4 * max(x.words for x in g.graphs.values() if x.batch == len(entries))
+                self.last_d2h_bytes = 4 * len(entries)
+                return SamplerOutput(tokens, None, None)
+        logits = self.step(entries)
+        out = sampler.sample(logits, rows)
+        self.last_d2h_bytes = 4 * len(rows)
+        return out

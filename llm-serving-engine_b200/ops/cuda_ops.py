@@ -46,6 +46,15 @@ class CudaOps:
             self.ext.load_attention_library(build.attention_library(head_dim), head_dim)
             self._attn_loaded.add(head_dim)
 
+    def reserve_attention_scratch(self, head_dim: int, max_decode: int, num_heads: int,
+                                  max_splits: int = 64) -> None:
+        """Allocate the partial-result buffer of split-context attention once, at its largest."""
+        need = int(self.ext.attention_scratch_floats(head_dim, max_decode, num_heads, max_splits))
+        if self._scratch is None or self._scratch.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("attention scratch must be reserved before graph capture")
+            self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+
     # ------------------------------------------------------------------ pointwise
     def embedding(self, token_ids, table):
         out = torch.empty(token_ids.shape[0], table.shape[1], dtype=torch.float32, device=table.device)
@@ -132,9 +141,7 @@ class CudaOps:
             n_dec, num_kv_heads, step.max_decode_ctx)
         scratch = None
         if n_dec and splits > 1:
-            need = int(self.ext.attention_scratch_floats(head_dim, n_dec, num_heads, splits))
-            if self._scratch is None or self._scratch.numel() < need:
-                self._scratch = torch.empty(need, dtype=torch.float32, device=qkv.device)
+            self.reserve_attention_scratch(head_dim, n_dec, num_heads, splits)
             scratch = self._scratch
         self.ext.paged_attention(
             qkv, out, k_pages, v_pages, num_heads, num_kv_heads, head_dim, float(scale),

@@ -69,6 +69,11 @@ class PagedAttention(Mixer):
         s = self.spec
         return PagedKVNeed(s.num_kv_heads, s.head_dim, s.window)
 
+    def reserve(self, max_seqs: int) -> None:
+        """Allocate kernel scratch for up to ``max_seqs`` single-token sequences in a step."""
+        if hasattr(self.ops, "reserve_attention_scratch"):
+            self.ops.reserve_attention_scratch(self.spec.head_dim, max_seqs, self.spec.num_heads)
+
     # work lists depend only on the batch, the kernels' tile size and the group's page size
     def plan_key(self):
         return ("attention", self.env.dtype, self.spec.head_dim)

@@ -160,6 +160,9 @@ class Mixer(Part):
     def plan_key(self):
         return None
 
+    def reserve(self, max_seqs: int) -> None:
+        """Allocate whatever scratch the mixer's kernels need for ``max_seqs`` sequences a step."""
+
     def plan_step(self, host_step, group):
         return {}
 

@@ -1,0 +1,137 @@
+"""The engine's host logic end to end on the CPU, with plain PyTorch kernels behind it."""
+
+import pytest
+
+import plain_llama
+from conftest import TINY
+from plain_ops import PlainOps
+
+
+def engine(folder, name, **kw):
+    from llmserve_b200 import EngineConfig, LLMEngine
+
+    d = dict(model=str(folder), dtype="float32", device="cpu", block_size=TINY[name]["page_tokens"],
+             num_kv_blocks=64, max_model_len=TINY[name]["max_position_embeddings"], max_num_seqs=8)
+    d.update(kw)
+    return LLMEngine(EngineConfig(**d), ops=PlainOps())
+
+
+def run_all(eng):
+    done = {}
+    while eng.has_unfinished_requests():
+        for o in eng.step():
+            if o.finished:
+                done[o.request_id] = o
+        eng.manager.check_invariants()
+    return done
+
+
+PROMPTS = [[5, 9, 200, 31, 7], list(range(40, 57)), [3] * 33, [100, 2]]
+
+
+def test_greedy_generation_matches_the_plain_model(sharp_dirs):
+    from llmserve_b200 import SamplingParams
+
+    eng = engine(sharp_dirs["A"], "A")
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    ids = [eng.add_request(p, sp) for p in PROMPTS]
+    done = run_all(eng)
+    for rid, p in zip(ids, PROMPTS):
+        assert done[rid].outputs[0].token_ids == plain_llama.greedy(sharp_dirs["A"], p, 8)
+        assert done[rid].outputs[0].finish_reason == "length"
+    assert eng.manager.usage() == 0.0 and eng.stats()["num_running"] == 0
+
+
+def test_portions_and_preemption_do_not_change_the_tokens(sharp_dirs):
+    from llmserve_b200 import SamplingParams
+
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    base = engine(sharp_dirs["B"], "B")
+    ids = [base.add_request(p, sp) for p in PROMPTS]
+    done = run_all(base)
+    want = [done[i].outputs[0].token_ids for i in ids]
+    small = engine(sharp_dirs["B"], "B", max_num_batched_tokens=8)  # many portions
+    ids = [small.add_request(p, sp) for p in PROMPTS]
+    done = run_all(small)
+    assert [done[i].outputs[0].token_ids for i in ids] == want
+    tight = engine(sharp_dirs["B"], "B", num_kv_blocks=9, max_num_batched_tokens=16)  # 72 tokens of cache
+    ids = [tight.add_request(p, sp) for p in PROMPTS]
+    done = run_all(tight)
+    assert tight.scheduler.num_preemptions > 0
+    assert [done[i].outputs[0].token_ids for i in ids] == want
+
+
+def test_seeded_sampling_does_not_depend_on_the_batch(sharp_dirs):
+    from llmserve_b200 import SamplingParams
+
+    sp = SamplingParams(temperature=0.8, top_k=50, seed=123, max_tokens=10, ignore_eos=True)
+    alone = engine(sharp_dirs["A"], "A")
+    rid = alone.add_request(PROMPTS[1], sp)
+    want = run_all(alone)[rid].outputs[0].token_ids
+    busy = engine(sharp_dirs["A"], "A", max_num_batched_tokens=8)
+    busy.add_request(PROMPTS[0], SamplingParams(temperature=1.0, max_tokens=9, ignore_eos=True))
+    rid = busy.add_request(PROMPTS[1], sp)
+    busy.add_request(PROMPTS[2], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    assert run_all(busy)[rid].outputs[0].token_ids == want
+    assert len(set(want)) > 1
+
+
+def test_stop_tokens_min_tokens_eos_logprobs_abort(sharp_dirs):
+    from llmserve_b200 import SamplingParams
+
+    eng = engine(sharp_dirs["A"], "A")
+    free = plain_llama.greedy(sharp_dirs["A"], PROMPTS[0], 6)
+    k = next(i for i in range(1, 6) if free[i] not in free[:i])  # first new token after the first
+    rid = eng.add_request(PROMPTS[0], SamplingParams(temperature=0, max_tokens=6, stop_token_ids=[free[k]]))
+    o = run_all(eng)[rid].outputs[0]
+    assert o.token_ids == free[: k + 1] and o.finish_reason == "stop" and o.stop_reason == free[k]
+    # the same stop token is banned until min_tokens is reached, so the continuation changes there
+    rid = eng.add_request(PROMPTS[0], SamplingParams(temperature=0, max_tokens=6, min_tokens=k + 2,
+                                                     stop_token_ids=[free[k]]))
+    o = run_all(eng)[rid].outputs[0]
+    assert o.token_ids[:k] == free[:k] and o.token_ids[k] != free[k] and len(o.token_ids) >= k + 2
+    rid = eng.add_request(PROMPTS[1], SamplingParams(temperature=0, max_tokens=3, logprobs=2, ignore_eos=True))
+    o = run_all(eng)[rid].outputs[0]
+    assert len(o.logprobs) == 3 and all(lp <= 0 for lp in o.logprobs)
+    assert o.top_logprobs[0][0][0] == o.token_ids[0] and abs(o.top_logprobs[0][0][1] - o.logprobs[0]) < 1e-5
+    rid = eng.add_request(PROMPTS[2], SamplingParams(max_tokens=30, ignore_eos=True))
+    eng.step()
+    assert eng.manager.usage() > 0
+    eng.abort_request(rid)
+    assert eng.manager.usage() == 0.0 and not eng.has_unfinished_requests()
+
+
+def test_intake_errors(tiny_dirs):
+    from llmserve_b200 import SamplingParams
+
+    eng = engine(tiny_dirs["A"], "A", num_kv_blocks=4)
+    with pytest.raises(ValueError, match="empty"):
+        eng.add_request([])
+    with pytest.raises(ValueError, match="max_model_len"):
+        eng.add_request([1] * 256)
+    with pytest.raises(ValueError, match="never fit"):
+        eng.add_request([1] * 60, SamplingParams(max_tokens=10))
+    with pytest.raises(ValueError, match="token ids"):
+        eng.add_request([1, 256])
+    with pytest.raises(ValueError, match="tokenizer"):
+        eng.add_request("hello")
+    eng.add_request([1, 2], request_id="x")
+    with pytest.raises(ValueError, match="duplicate"):
+        eng.add_request([1, 2], request_id="x")
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0)
+    with pytest.raises(ValueError):
+        SamplingParams(n=2)
+
+
+def test_llm_generate_returns_outputs_in_input_order(sharp_dirs):
+    from llmserve_b200 import LLM, SamplingParams
+
+    llm = LLM(str(sharp_dirs["C"]), ops=PlainOps(), dtype="float32", device="cpu", block_size=32,
+              num_kv_blocks=16, max_model_len=256, max_num_seqs=2)
+    outs = llm.generate(PROMPTS[:3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert [o.prompt_token_ids for o in outs] == PROMPTS[:3]
+    for o, p in zip(outs, PROMPTS):
+        assert o.outputs[0].token_ids == plain_llama.greedy(sharp_dirs["C"], p, 4)
+    one = llm.generate(PROMPTS[3], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    assert len(one) == 1 and len(one[0].outputs[0].token_ids) == 2

@@ -37,6 +37,7 @@ class EngineConfig:
     enable_prefix_caching: bool = False  # not built: pages are reused, their contents are not
     seed: int = 0  # weights seed of "random:<alias>" models
     cuda_graphs: bool = True  # replay captured graphs for steps of single tokens only
+    config_overrides: dict | None = None  # config.json keys to replace in a "random:<alias>" model
 
     def scheduler_config(self) -> SchedulerConfig:
         return SchedulerConfig(
@@ -73,7 +74,7 @@ class LLMEngine:
             ops = get_ops(cfg.device)
         self.ops = ops
         if cfg.model.startswith("random:"):
-            d = preset_config_dict(cfg.model.split(":", 1)[1])
+            d = {**preset_config_dict(cfg.model.split(":", 1)[1]), **(cfg.config_overrides or {})}
             arch = architecture_for(d)
             mcfg = arch.config_cls.from_dict(d)
             self.model = build_model(

@@ -404,47 +404,56 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
     }
   }
 
-  for (int j0 = lo + warp * KPI; j0 < hi; j0 += DEC_WARPS * KPI) {
-    const int j = j0 + slot;
-    const bool ok = j < hi;
-    size_t base = 0;
-    if (ok) {
+  // U passes of the warp are in flight together: all their loads are issued before any arithmetic.
+  constexpr int U = (GT * CPL <= 2) ? 4 : 2;
+  for (int j0 = lo + warp * KPI; j0 < hi; j0 += DEC_WARPS * KPI * U) {
+    Vec16<T> kv[U][CPL], vv[U][CPL];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * DEC_WARPS * KPI + slot;
+      ok[u] = j < hi;
+      // a key past the end re-reads the last valid one (its result is dropped): no branch, so
+      // every load of the U passes is issued before the first use
       int pi, off;
-      page_of(j, a.page_tokens, page_shift, pi, off);
-      base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
-    }
-    Vec16<T> kv[CPL], vv[CPL];
+      page_of(min(j, hi - 1), a.page_tokens, page_shift, pi, off);
+      const size_t base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
 #pragma unroll
-    for (int c = 0; c < CPL; ++c) {
-      const int ch = li + c * LPK;
-      if (ok && ch < NCHUNK) {
-        kv[c] = load16(kp + base + ch * VEC);
-        vv[c] = load16(vp + base + ch * VEC);
-      } else {
+      for (int c = 0; c < CPL; ++c) {
+        const int ch = li + c * LPK;
+        if (NCHUNK % LPK == 0 || ch < NCHUNK) {
+          kv[u][c] = load16(kp + base + ch * VEC);
+          vv[u][c] = load16(vp + base + ch * VEC);
+        } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) kv[c].v[e] = vv[c].v[e] = Num<T>::from_float(0.f);
+          for (int e = 0; e < VEC; ++e) kv[u][c].v[e] = vv[u][c].v[e] = Num<T>::from_float(0.f);
+        }
       }
     }
 #pragma unroll
-    for (int gq = 0; gq < GT; ++gq) {
-      float d = 0.f;
+    for (int u = 0; u < U; ++u) {
 #pragma unroll
-      for (int c = 0; c < CPL; ++c)
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) d = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[c].v[e]), d);
-#pragma unroll
-      for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-      if (ok) {  // uniform over the LPK lanes of a key
-        const float m_new = fmaxf(m[gq], d);
-        const float corr = Exp<T>::f(m[gq] - m_new);
-        const float p = Exp<T>::f(d - m_new);
-        l[gq] = l[gq] * corr + p;
+      for (int gq = 0; gq < GT; ++gq) {
+        float d = 0.f;
 #pragma unroll
         for (int c = 0; c < CPL; ++c)
 #pragma unroll
           for (int e = 0; e < VEC; ++e)
-            acc[gq][c][e] = fmaf(p, Num<T>::to_float(vv[c].v[e]), acc[gq][c][e] * corr);
-        m[gq] = m_new;
+            d = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[u][c].v[e]), d);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        if (ok[u]) {  // uniform over the LPK lanes of a key
+          const float m_new = fmaxf(m[gq], d);
+          const float corr = Exp<T>::f(m[gq] - m_new);
+          const float p = Exp<T>::f(d - m_new);
+          l[gq] = l[gq] * corr + p;
+#pragma unroll
+          for (int c = 0; c < CPL; ++c)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e)
+              acc[gq][c][e] = fmaf(p, Num<T>::to_float(vv[u][c].v[e]), acc[gq][c][e] * corr);
+          m[gq] = m_new;
+        }
       }
     }
   }

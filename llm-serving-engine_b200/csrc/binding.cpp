@@ -161,6 +161,45 @@ void gemm_f32(const Tensor& a, const Tensor& w, const OptTensor& bias, Tensor& o
        "gemm_f32");
 }
 
+// A host-mapped int that kernels set when a bounded wait runs out; the host reads it without a copy.
+int* error_flag() {
+  static int* flag = nullptr;
+  if (!flag) {
+    TORCH_CHECK(cudaHostAlloc(&flag, sizeof(int), cudaHostAllocMapped) == cudaSuccess,
+                "cannot allocate the kernels' error flag");
+    *flag = 0;
+  }
+  return flag;
+}
+
+int64_t kernel_error() { return *error_flag(); }
+void clear_kernel_error() { *error_flag() = 0; }
+
+int64_t gemm_bf16_skinny_max_rows() { return lse_gemm_bf16_skinny_max_rows(); }
+
+void gemm_bf16_skinny(const Tensor& a, const Tensor& w, const OptTensor& bias, Tensor& out,
+                      bool atomic_add, int64_t split_k) {
+  check_cuda(a, "a");
+  check_cuda(w, "w");
+  check_cuda(out, "out");
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && w.scalar_type() == torch::kBFloat16,
+              "gemm_bf16_skinny: a and w must be bfloat16");
+  TORCH_CHECK(a.dim() == 2 && w.dim() == 2 && out.dim() == 2 && a.size(1) == w.size(1) &&
+                  out.size(0) == a.size(0) && out.size(1) == w.size(0),
+              "gemm_bf16_skinny: need a [T, K], w [N, K], out [T, N]");
+  const void* b = nullptr;
+  if (bias) {
+    check_cuda(*bias, "bias");
+    TORCH_CHECK(bias->scalar_type() == torch::kBFloat16 && bias->numel() == w.size(0),
+                "gemm_bf16_skinny: bias must be bfloat16 [N]");
+    b = bias->data_ptr();
+  }
+  done(lse_gemm_bf16_skinny(a.data_ptr(), w.data_ptr(), b, out.data_ptr(), dtype_code(out, "out"),
+                            atomic_add ? 1 : 0, (int)a.size(0), (int)w.size(0), (int)a.size(1),
+                            (int)split_k, error_flag(), stream()),
+       "gemm_bf16_skinny");
+}
+
 // ------------------------------------------------------------------ attention libraries
 struct AttnLib {
   void* handle;
@@ -355,6 +394,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_kv_write", &rope_kv_write);
   m.def("silu_mul", &silu_mul);
   m.def("gemm_f32", &gemm_f32);
+  m.def("gemm_bf16_skinny", &gemm_bf16_skinny);
+  m.def("gemm_bf16_skinny_max_rows", &gemm_bf16_skinny_max_rows);
+  m.def("kernel_error", &kernel_error);
+  m.def("clear_kernel_error", &clear_kernel_error);
   m.def("load_attention_library", &load_attention_library);
   m.def("attention_q_tile", &attention_q_tile);
   m.def("attention_scratch_floats", &attention_scratch_floats);

@@ -1,0 +1,326 @@
+// bfloat16 matrix product for few rows (decode), on the 5th-generation tensor cores:
+//   out[T, N] (+)= a[T, K] . w[N, K]^T        T <= 256, float32 accumulation
+//
+// With few rows the product is bound by streaming the weights once from HBM, so the operands are
+// swapped: the *weights* are the 128-row operand of tcgen05.mma (M = 128 output features per
+// block) and the tokens are its N dimension (16..256). Both operands are K-major in global memory
+// already, so TMA brings [rows, 64] tiles straight into 128-byte-swizzled shared memory. One
+// elected thread issues tcgen05.mma (cta_group::1, kind::f16) with the accumulator [128 x T] in
+// tensor memory; another thread runs the TMA pipeline; all four warps read the accumulator back
+// with tcgen05.ld and write out[t, n] with n across lanes (coalesced).
+//
+// K may be split over gridDim.y blocks (to fill the GPU when N/128 is small); partial sums are then
+// added with float32 atomics into `out`, which the caller has zeroed or which already holds the
+// residual stream (accumulate = 1).
+//
+// Every wait on an mbarrier is bounded: on expiry the block records an error code in *error_flag
+// and leaves through the normal teardown (tensor memory is released).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lse {
+namespace tc {
+
+constexpr int BM = 128;        // output features per block (MMA M)
+constexpr int BK = 64;         // k elements per stage: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+// Bounded wait. Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+      "%4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart (tile base aligned to 1024 bytes).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                   // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
+  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M x N.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc,
+                                     uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+struct Params {
+  int T, N, K;
+  int chunks_per_split;   // k stages each block of a split runs
+  int out_dtype;          // LSE_F32 or LSE_BF16
+  int atomic_add;         // add into out with float32 atomics (out float32)
+  void* out;
+  const bf16* bias;       // [N] or nullptr (added by split 0 only)
+  int* error_flag;
+};
+
+// NT: tokens per block, padded (MMA N): 16, 32, 64, 128 or 256. STAGES: pipeline depth.
+template <int NT, int STAGES>
+__global__ void __launch_bounds__(128)
+skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                   const Params p) {
+  constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = NT * BK * 2;
+  constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // 1024-byte alignment of the tiles is required by the swizzled descriptors
+  unsigned char* base = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* w_tiles = base;
+  unsigned char* a_tiles = base + STAGES * W_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(a_tiles + STAGES * A_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_full + 1);
+  __shared__ int failed;
+  __shared__ int issued;  // stages the producer has requested from TMA
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM;
+  const int total_chunks = (p.K + BK - 1) / BK;
+  const int c_begin = blockIdx.y * p.chunks_per_split;
+  const int c_end = min(total_chunks, c_begin + p.chunks_per_split);
+  const int my_chunks = max(0, c_end - c_begin);
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    issued = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {  // one warp allocates tensor memory for the block
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = *tmem_slot;
+
+  // The other lanes of the two role warps wait at __syncwarp, not on a barrier: a lane that spins
+  // in try_wait would take turns with the role lane of its own warp and stall the pipeline.
+  if (my_chunks > 0 && warp < 2) {
+    if (warp == 0 && lane == 0) {
+      // ---- TMA producer
+      for (int c = 0; c < my_chunks; ++c) {
+        const int s = c % STAGES;
+        if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) - 1) & 1)) {
+          atomicExch(&failed, 1);
+          break;
+        }
+        mbar_expect_tx(&full[s], W_BYTES + A_BYTES);
+        const int k = (c_begin + c) * BK;
+        tma_load_2d(w_tiles + s * W_BYTES, &map_w, &full[s], k, n0);
+        tma_load_2d(a_tiles + s * A_BYTES, &map_a, &full[s], k, 0);
+        issued = c + 1;
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---- MMA issuer
+      constexpr uint32_t idesc = instr_desc(BM, NT);
+      bool ok = true;
+      for (int c = 0; c < my_chunks && ok; ++c) {
+        const int s = c % STAGES;
+        ok = mbar_wait(&full[s], (c / STAGES) & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t da = smem_desc(smem_u32(w_tiles + s * W_BYTES));
+        const uint64_t db = smem_desc(smem_u32(a_tiles + s * A_BYTES));
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+          // 16 k-elements = 32 bytes further along the swizzled row: +2 in the address field
+          umma(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (c > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);  // arrives when the MMAs that read this stage are done
+      }
+      if (!ok) atomicExch(&failed, 2);
+      umma_commit(accum_full);
+    }
+    __syncwarp();
+  }
+  // ---- epilogue: all four warps; warp w owns accumulator rows (TMEM lanes) 32w .. 32w+31
+  bool acc_ok = true;
+  if (my_chunks > 0) {
+    acc_ok = mbar_wait(accum_full, 0);
+    if (!acc_ok) atomicExch(&failed, 3);
+  }
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  __syncthreads();  // every role is done; `failed` is final and read alike by all threads
+  const bool good = failed == 0;
+  if (my_chunks > 0 && good) {
+    const int n = n0 + warp * 32 + lane;
+    const float bias = (p.bias && blockIdx.y == 0 && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+    for (int t0 = 0; t0 < NT; t0 += 16) {
+      if (t0 >= p.T) break;  // uniform
+      uint32_t v[16];
+      const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)t0;
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
+          "%15}, [%16];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+            "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+            "=r"(v[14]), "=r"(v[15])
+          : "r"(taddr));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int t = t0 + j;
+          if (t >= p.T) break;
+          const float val = __uint_as_float(v[j]) + bias;
+          const size_t o = (size_t)t * p.N + n;
+          if (p.atomic_add) atomicAdd(reinterpret_cast<float*>(p.out) + o, val);
+          else if (p.out_dtype == LSE_F32) reinterpret_cast<float*>(p.out)[o] = val;
+          else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
+        }
+      }
+    }
+  }
+  if (threadIdx.x == 0 && !good) {
+    if (p.error_flag) atomicExch(p.error_flag, 100 + failed);
+    // copies that were requested must land before the block's shared memory is given up
+    for (int c = max(0, issued - STAGES); c < issued; ++c)
+      if (!mbar_wait(&full[c % STAGES], (c / STAGES) & 1)) break;
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// [rows, K] bfloat16 row-major; box = [box_rows, 64 k]; rows or k past the edge read as zero.
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NT, int STAGES>
+static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Params& p, dim3 grid,
+                  cudaStream_t stream) {
+  constexpr int smem = STAGES * (BM * BK * 2 + NT * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(skinny_gemm_kernel<NT, STAGES>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return LSE_LAUNCH_FAILED;
+    configured = true;
+  }
+  skinny_gemm_kernel<NT, STAGES><<<grid, 128, smem, stream>>>(mw, ma, p);
+  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+}
+
+}  // namespace tc
+}  // namespace lse
+
+using namespace lse;
+
+extern "C" int lse_gemm_bf16_skinny_max_rows(void) { return 256; }
+
+extern "C" int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out,
+                                    int out_dtype, int atomic_add, int T, int N, int K, int split_k,
+                                    int* error_flag, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return LSE_OK;
+  if (T > 256 || K <= 0 || K % 8 || split_k < 1) return LSE_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) return LSE_BAD_ARGUMENT;
+  if (atomic_add && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
+  const int chunks = (K + tc::BK - 1) / tc::BK;
+  if (split_k > chunks) split_k = chunks;
+  if (split_k > 1 && !atomic_add) return LSE_BAD_ARGUMENT;
+  const int nt = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  CUtensorMap mw, ma;
+  if (!tc::make_map(&mw, w, N, K, tc::BM) || !tc::make_map(&ma, a, T, K, nt)) return LSE_LAUNCH_FAILED;
+  tc::Params p;
+  p.T = T; p.N = N; p.K = K;
+  p.chunks_per_split = (chunks + split_k - 1) / split_k;
+  p.out_dtype = out_dtype; p.atomic_add = atomic_add; p.out = out;
+  p.bias = reinterpret_cast<const bf16*>(bias); p.error_flag = error_flag;
+  dim3 grid((N + tc::BM - 1) / tc::BM, (chunks + p.chunks_per_split - 1) / p.chunks_per_split);
+  // four stages leave room for several blocks per SM, which hides each block's start and end
+  switch (nt) {
+    case 16: return tc::launch<16, 4>(mw, ma, p, grid, stream);
+    case 32: return tc::launch<32, 4>(mw, ma, p, grid, stream);
+    case 64: return tc::launch<64, 4>(mw, ma, p, grid, stream);
+    case 128: return tc::launch<128, 6>(mw, ma, p, grid, stream);
+    default: return tc::launch<256, 4>(mw, ma, p, grid, stream);
+  }
+}

@@ -42,6 +42,16 @@ int lse_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_
 int lse_gemm_f32(const float* a, const float* w, const float* bias, float* out, int T, int N, int K,
                  cudaStream_t stream);
 
+// bfloat16 product for few rows on tcgen05 tensor cores fed by TMA (gemm_bf16_tc.cu):
+//   out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]),  T <= lse_gemm_bf16_skinny_max_rows(), K % 8 == 0.
+// out_dtype LSE_F32 or LSE_BF16. With atomic_add = 1 (out float32) results are added to what out
+// holds, and K may be split over split_k blocks. error_flag (device-visible int, may be null)
+// receives a non-zero code if a bounded wait inside the kernel ran out.
+int lse_gemm_bf16_skinny_max_rows(void);
+int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out, int out_dtype,
+                         int atomic_add, int T, int N, int K, int split_k, int* error_flag,
+                         cudaStream_t stream);
+
 // Sampling. One token per row of logits [R, V] (float32, row stride V).
 //   temperature[r] < 1e-5 selects the largest logit (lowest index on ties). Otherwise the row is
 //   divided by its temperature, cut to top_k / top_p / min_p, and a token is drawn by the

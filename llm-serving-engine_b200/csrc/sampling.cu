@@ -9,7 +9,7 @@
 
 namespace lse {
 
-constexpr int SAMPLE_THREADS = 512;
+constexpr int SAMPLE_THREADS = 1024;
 
 // order-preserving map float -> uint32
 __device__ __forceinline__ uint32_t float_key(float f) {
@@ -79,7 +79,17 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const float temp = temperature[r];
   if (temp < 1e-5f) {
     ArgMax a = {-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) a = better(a, ArgMax{row[i], i});
+    if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + i);
+        a = better(a, ArgMax{v.x, i});
+        a = better(a, ArgMax{v.y, i + 1});
+        a = better(a, ArgMax{v.z, i + 2});
+        a = better(a, ArgMax{v.w, i + 3});
+      }
+    } else {
+      for (int i = threadIdx.x; i < V; i += blockDim.x) a = better(a, ArgMax{row[i], i});
+    }
     a = block_argmax(a, as);
     if (threadIdx.x == 0) out[r] = a.i;
     return;

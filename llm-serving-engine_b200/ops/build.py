@@ -27,7 +27,7 @@ from pathlib import Path
 CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr"]
-CORE_CU = ["pointwise.cu", "gemm_f32.cu", "sampling.cu"]
+CORE_CU = ["pointwise.cu", "gemm_f32.cu", "gemm_bf16_tc.cu", "sampling.cu"]
 CORE_HEADERS = ["common.cuh", "kernels.h", "attention_args.h", "status.h"]
 
 _core = None

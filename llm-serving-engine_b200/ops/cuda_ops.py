@@ -32,6 +32,8 @@ class CudaOps:
         self._scratch: torch.Tensor | None = None
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.force_simt_attention = False
+        self.use_skinny_gemm = True
+        self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
         self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
 
     # ------------------------------------------------------------------ capabilities
@@ -54,6 +56,13 @@ class CudaOps:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("attention scratch must be reserved before graph capture")
             self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+
+    def check_kernel_errors(self) -> None:
+        """Raise if a kernel recorded that one of its bounded waits ran out."""
+        code = int(self.ext.kernel_error())
+        if code:
+            self.ext.clear_kernel_error()
+            raise RuntimeError(f"a CUDA kernel of llmserve_b200 gave up waiting (code {code})")
 
     # ------------------------------------------------------------------ pointwise
     def embedding(self, token_ids, table):
@@ -87,15 +96,30 @@ class CudaOps:
             return out if out_dtype == torch.float32 else out.to(out_dtype)
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise TypeError(f"linear: unsupported dtypes {a.dtype} x {w.dtype}")
+        T, K = a.shape
+        N = w.shape[0]
+        if (self.use_skinny_gemm and T <= self.skinny_max_rows and K % 8 == 0
+                and out_dtype == torch.float32):
+            # few rows: stream the weights once through the tcgen05 kernel
+            tiles, chunks = -(-N // 128), -(-K // 64)
+            split = 1
+            if out_dtype == torch.float32:
+                split = max(1, min(2 * self.num_sms // tiles, chunks // 4))
+            if split > 1:
+                out = torch.zeros(T, N, dtype=torch.float32, device=a.device)
+            else:
+                out = torch.empty(T, N, dtype=out_dtype, device=a.device)
+            self.ext.gemm_bf16_skinny(a, w, bias, out, split > 1, split)
+            self.launches += 1
+            return out
         if out_dtype == torch.float32:
             out = torch.mm(a, w.t(), out_dtype=torch.float32)
             if bias is not None:
                 out += bias.float()
             return out
-        out = torch.mm(a, w.t())
         if bias is not None:
-            out += bias
-        return out
+            return torch.addmm(bias, a, w.t())  # bias added before the one rounding to bfloat16
+        return torch.mm(a, w.t())
 
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
@@ -125,12 +149,12 @@ class CudaOps:
         }
 
     def decode_splits(self, num_decode, num_kv_heads, max_ctx):
-        """Context partitions per (sequence, head) so that the grid fills the GPU about twice."""
+        """Context partitions per (sequence, head): about six blocks per SM, 64 keys or more each."""
         if num_decode == 0:
             return 1
         blocks = num_decode * num_kv_heads
-        want = max(1, (2 * self.num_sms + blocks - 1) // blocks)
-        return int(max(1, min(want, (max_ctx + 255) // 256, 64)))
+        want = max(1, (6 * self.num_sms + blocks - 1) // blocks)
+        return int(max(1, min(want, (max_ctx + 63) // 64, 64)))
 
     def paged_attention(self, qkv, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan):

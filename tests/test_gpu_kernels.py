@@ -84,14 +84,33 @@ def test_gemm_f32_is_true_float32_and_batch_invariant(ops, T, N, K, bias):
     assert torch.equal(alone[0], got[T // 2])
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16"])
-@pytest.mark.parametrize("T,N,K", [(1, 48, 64), (9, 520, 200), (300, 136, 1000)])
-def test_linear_bf16(ops, dtype, T, N, K):
+@pytest.mark.parametrize("T,N,K", [(1, 48, 64), (9, 520, 200), (16, 128, 64), (17, 2048, 2048),
+                                   (64, 136, 1000), (100, 384, 8192), (256, 1000, 520), (300, 136, 1000)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_bf16(ops, T, N, K, bias):
+    """Few rows run the tcgen05 kernel (with and without split K), many rows the library."""
     a, w = rnd(T, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2)
+    b = rnd(N, dtype=torch.bfloat16, seed=3) if bias else None
+    ref = a.double() @ w.double().T + (0 if b is None else b.double())
     for od in (torch.bfloat16, torch.float32):
-        got = ops.linear(a.cuda(), w.cuda(), None, out_dtype=od)
-        assert got.dtype == od
-        close(got, a.float() @ w.float().T, "bfloat16", rel16=0.006)
+        got = ops.linear(a.cuda(), w.cuda(), None if b is None else b.cuda(), out_dtype=od)
+        assert got.dtype == od and got.shape == (T, N)
+        err = (got.double().cpu() - ref).abs().max().item()
+        # float32 accumulation: the error is the rounding of the output only (bf16) or ~1e-6 relative
+        bound = (2.0**-8 if od == torch.bfloat16 else 3e-6 * K**0.5) * ref.abs().max().item()
+        assert err <= bound, (od, err, bound)
+    ops.check_kernel_errors()
+
+
+def test_skinny_gemm_sees_every_k_and_every_row(ops):
+    """One-hot inputs: a wrong swizzle, k offset or row mapping shows up as a misplaced value."""
+    T, N, K = 5, 300, 328
+    w = (torch.arange(N * K, dtype=torch.float32).reshape(N, K) % 251 - 125).to(torch.bfloat16)
+    for k in (0, 15, 16, 63, 64, 200, 327):
+        a = torch.zeros(T, K, dtype=torch.bfloat16)
+        a[:, k] = torch.arange(1, T + 1).to(torch.bfloat16)
+        got = ops.linear(a.cuda(), w.cuda(), None, out_dtype=torch.float32).cpu()
+        assert torch.equal(got, a.float() @ w.float().T), k
 
 
 def paged_case(nseq, q_lens, ctx_lens, nq, nk, D, page, dtype, seed=0, shuffle=True):

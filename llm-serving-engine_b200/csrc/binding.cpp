@@ -89,10 +89,12 @@ void add_rmsnorm(Tensor& x, const OptTensor& residual, const Tensor& weight, dou
        "add_rmsnorm");
 }
 
-void rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tensor& positions,
-                   const Tensor& token_seq, const OptTensor& cos, const OptTensor& sin,
-                   const OptTensor& k_pages, const OptTensor& v_pages, const Tensor& block_tables,
-                   int64_t page_tokens) {
+// Returns the rotated queries: a view of qkv's first nq*D columns when qkv already has the pages'
+// dtype, or a new [T, nq*D] tensor of `q_dtype` when qkv holds float32 sums.
+Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tensor& positions,
+                     const Tensor& token_seq, const OptTensor& cos, const OptTensor& sin,
+                     const OptTensor& k_pages, const OptTensor& v_pages, const Tensor& block_tables,
+                     int64_t page_tokens, bool q_bf16) {
   check_cuda(qkv, "qkv");
   check_i32(positions, "positions");
   check_i32(token_seq, "token_seq");
@@ -101,6 +103,9 @@ void rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tensor&
   const int T = (int)qkv.size(0);
   TORCH_CHECK(positions.size(0) == T && token_seq.size(0) == T, "rope_kv_write: lengths differ");
   TORCH_CHECK(block_tables.dim() == 2, "rope_kv_write: block_tables must be [sequences, blocks]");
+  const int in_code = dtype_code(qkv, "qkv");
+  const int out_code = q_bf16 ? LSE_BF16 : LSE_F32;
+  TORCH_CHECK(in_code == out_code || in_code == LSE_F32, "rope_kv_write: bfloat16 qkv cannot give float32 q");
   const float *c = nullptr, *s = nullptr;
   if (cos) {
     TORCH_CHECK(sin.has_value(), "rope_kv_write: cos without sin");
@@ -116,30 +121,33 @@ void rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tensor&
     TORCH_CHECK(v_pages.has_value(), "rope_kv_write: k_pages without v_pages");
     check_cuda(*k_pages, "k_pages");
     check_cuda(*v_pages, "v_pages");
-    TORCH_CHECK(k_pages->scalar_type() == qkv.scalar_type() &&
-                    v_pages->scalar_type() == qkv.scalar_type(),
-                "rope_kv_write: pages and qkv differ in dtype");
+    TORCH_CHECK(dtype_code(*k_pages, "k_pages") == out_code && dtype_code(*v_pages, "v_pages") == out_code,
+                "rope_kv_write: pages and q differ in dtype");
     TORCH_CHECK(k_pages->dim() == 4 && k_pages->size(1) == nk && k_pages->size(2) == page_tokens &&
                     k_pages->size(3) == D && v_pages->sizes() == k_pages->sizes(),
                 "rope_kv_write: pages must be [pages, kv_heads, page_tokens, head_dim]");
     kp = k_pages->data_ptr();
     vp = v_pages->data_ptr();
   }
-  done(lse_rope_kv_write(qkv.data_ptr(), dtype_code(qkv, "qkv"), T, (int)nq, (int)nk, (int)D,
+  Tensor q = in_code == out_code
+                 ? qkv.narrow(1, 0, nq * D)
+                 : torch::empty({T, nq * D}, qkv.options().dtype(torch::kBFloat16));
+  done(lse_rope_kv_write(qkv.data_ptr(), in_code, q.data_ptr(), out_code, T, (int)nq, (int)nk, (int)D,
                          positions.data_ptr<int>(), token_seq.data_ptr<int>(), c, s, kp, vp,
                          block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens,
                          stream()),
        "rope_kv_write");
+  return q;
 }
 
 void silu_mul(const Tensor& gu, Tensor& out) {
   check_cuda(gu, "gu");
   check_cuda(out, "out");
   TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(1) == 2 * out.size(1) &&
-                  gu.size(0) == out.size(0) && gu.scalar_type() == out.scalar_type(),
-              "silu_mul: gu must be [T, 2I] and out [T, I] of the same dtype");
-  done(lse_silu_mul(gu.data_ptr(), out.data_ptr(), dtype_code(gu, "gu"), (int)gu.size(0),
-                    (int)out.size(1), stream()),
+                  gu.size(0) == out.size(0),
+              "silu_mul: gu must be [T, 2I] and out [T, I]");
+  done(lse_silu_mul(gu.data_ptr(), dtype_code(gu, "gu"), out.data_ptr(), dtype_code(out, "out"),
+                    (int)gu.size(0), (int)out.size(1), stream()),
        "silu_mul");
 }
 
@@ -178,7 +186,7 @@ void clear_kernel_error() { *error_flag() = 0; }
 int64_t gemm_bf16_skinny_max_rows() { return lse_gemm_bf16_skinny_max_rows(); }
 
 void gemm_bf16_skinny(const Tensor& a, const Tensor& w, const OptTensor& bias, Tensor& out,
-                      bool atomic_add, int64_t split_k) {
+                      bool atomic_add) {
   check_cuda(a, "a");
   check_cuda(w, "w");
   check_cuda(out, "out");
@@ -196,7 +204,7 @@ void gemm_bf16_skinny(const Tensor& a, const Tensor& w, const OptTensor& bias, T
   }
   done(lse_gemm_bf16_skinny(a.data_ptr(), w.data_ptr(), b, out.data_ptr(), dtype_code(out, "out"),
                             atomic_add ? 1 : 0, (int)a.size(0), (int)w.size(0), (int)a.size(1),
-                            (int)split_k, error_flag(), stream()),
+                            error_flag(), stream()),
        "gemm_bf16_skinny");
 }
 

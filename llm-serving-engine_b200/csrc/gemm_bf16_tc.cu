@@ -9,9 +9,11 @@
 // tensor memory; another thread runs the TMA pipeline; all four warps read the accumulator back
 // with tcgen05.ld and write out[t, n] with n across lanes (coalesced).
 //
-// K may be split over gridDim.y blocks (to fill the GPU when N/128 is small); partial sums are then
-// added with float32 atomics into `out`, which the caller has zeroed or which already holds the
-// residual stream (accumulate = 1).
+// The kernel is persistent: one block per SM walks a contiguous range of (tile, k stage) units. With
+// atomic_add the ranges are balanced over all blocks whatever N is (a tile's K may be shared by
+// several blocks) and partial sums are added with float32 atomics into `out`, which the caller
+// has zeroed or which already holds the residual stream. Without it every block runs whole tiles
+// and stores them.
 //
 // Every wait on an mbarrier is bounded: on expiry the block records an error code in *error_flag
 // and leaves through the normal teardown (tensor memory is released).
@@ -94,21 +96,42 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 
 struct Params {
   int T, N, K;
-  int chunks_per_split;   // k stages each block of a split runs
+  int tiles, chunks;      // output tiles of 128 features; k stages of 64 per tile
+  int whole_tiles;        // 1: every block runs whole tiles (plain stores); 0: balanced k ranges
   int out_dtype;          // LSE_F32 or LSE_BF16
   int atomic_add;         // add into out with float32 atomics (out float32)
   void* out;
-  const bf16* bias;       // [N] or nullptr (added by split 0 only)
+  const bf16* bias;       // [N] or nullptr (added with the first k stage of a tile)
   int* error_flag;
 };
 
+// Work of one block: units [u_begin, u_end) of the sequence (tile 0 stage 0, tile 0 stage 1, ...).
+__device__ __forceinline__ void block_range(const Params& p, long long& u_begin, long long& u_end) {
+  const long long G = gridDim.x, g = blockIdx.x;
+  if (p.whole_tiles) {
+    u_begin = (g * p.tiles / G) * p.chunks;
+    u_end = ((g + 1) * p.tiles / G) * p.chunks;
+  } else {
+    const long long U = (long long)p.tiles * p.chunks;
+    u_begin = g * U / G;
+    u_end = (g + 1) * U / G;
+  }
+}
+
+// Persistent, warp-specialised kernel. 192 threads: warp 0 runs the TMA pipeline, warp 1 issues the
+// MMAs, warps 2..5 read accumulators back and write the output. A block walks a contiguous range
+// of (tile, k stage) units; each maximal run of units of one tile is a *segment* with its own
+// accumulator in tensor memory. Two accumulators alternate, so the epilogue of one segment overlaps
+// the loads and MMAs of the next. A segment that covers all of K is stored; a partial one is added
+// to the output with float32 atomics.
 // NT: tokens per block, padded (MMA N): 16, 32, 64, 128 or 256. STAGES: pipeline depth.
 template <int NT, int STAGES>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(192)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                    const Params p) {
   constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = NT * BK * 2;
-  constexpr uint32_t TMEM_COLS = NT < 32 ? 32 : NT;
+  constexpr uint32_t ACC_COLS = NT < 16 ? 16 : NT;
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment of the tiles is required by the swizzled descriptors
   unsigned char* base = reinterpret_cast<unsigned char*>(
@@ -117,26 +140,30 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   unsigned char* a_tiles = base + STAGES * W_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(a_tiles + STAGES * A_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* accum_full = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_full + 1);
-  __shared__ int failed;
-  __shared__ int issued;  // stages the producer has requested from TMA
+  uint64_t* acc_full = empty + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  __shared__ volatile int failed;
+  __shared__ volatile int issued;  // stages the producer has requested from TMA
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM;
-  const int total_chunks = (p.K + BK - 1) / BK;
-  const int c_begin = blockIdx.y * p.chunks_per_split;
-  const int c_end = min(total_chunks, c_begin + p.chunks_per_split);
-  const int my_chunks = max(0, c_end - c_begin);
+  long long u_begin, u_end;
+  block_range(p, u_begin, u_end);
+  const int my_units = (int)(u_end - u_begin);
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     failed = 0;
     issued = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {  // one warp allocates tensor memory for the block
@@ -148,97 +175,131 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_d = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
-  // The other lanes of the two role warps wait at __syncwarp, not on a barrier: a lane that spins
-  // in try_wait would take turns with the role lane of its own warp and stall the pipeline.
-  if (my_chunks > 0 && warp < 2) {
-    if (warp == 0 && lane == 0) {
-      // ---- TMA producer
-      for (int c = 0; c < my_chunks; ++c) {
-        const int s = c % STAGES;
-        if (c >= STAGES && !mbar_wait(&empty[s], ((c / STAGES) - 1) & 1)) {
-          atomicExch(&failed, 1);
+  // Lanes 1..31 of the two role warps wait at __syncwarp, not on a barrier: a lane that spins in
+  // try_wait would take turns with the role lane of its own warp and stall the pipeline.
+  if (my_units > 0 && warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer: one (weights, activations) stage per unit
+      for (int it = 0; it < my_units && !failed; ++it) {
+        const int s = it % STAGES;
+        if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
+          failed = 1;
           break;
         }
+        const long long u = u_begin + it;
+        const int tile = (int)(u / p.chunks), kc = (int)(u - (long long)tile * p.chunks);
         mbar_expect_tx(&full[s], W_BYTES + A_BYTES);
-        const int k = (c_begin + c) * BK;
-        tma_load_2d(w_tiles + s * W_BYTES, &map_w, &full[s], k, n0);
-        tma_load_2d(a_tiles + s * A_BYTES, &map_a, &full[s], k, 0);
-        issued = c + 1;
+        tma_load_2d(w_tiles + s * W_BYTES, &map_w, &full[s], kc * BK, tile * BM);
+        tma_load_2d(a_tiles + s * A_BYTES, &map_a, &full[s], kc * BK, 0);
+        issued = it + 1;
       }
-    } else if (warp == 1 && lane == 0) {
-      // ---- MMA issuer
-      constexpr uint32_t idesc = instr_desc(BM, NT);
-      bool ok = true;
-      for (int c = 0; c < my_chunks && ok; ++c) {
-        const int s = c % STAGES;
-        ok = mbar_wait(&full[s], (c / STAGES) & 1);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = smem_desc(smem_u32(w_tiles + s * W_BYTES));
-        const uint64_t db = smem_desc(smem_u32(a_tiles + s * A_BYTES));
-#pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          // 16 k-elements = 32 bytes further along the swizzled row: +2 in the address field
-          umma(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (c > 0 || kk > 0) ? 1u : 0u);
-        }
-        umma_commit(&empty[s]);  // arrives when the MMAs that read this stage are done
-      }
-      if (!ok) atomicExch(&failed, 2);
-      umma_commit(accum_full);
     }
     __syncwarp();
-  }
-  // ---- epilogue: all four warps; warp w owns accumulator rows (TMEM lanes) 32w .. 32w+31
-  bool acc_ok = true;
-  if (my_chunks > 0) {
-    acc_ok = mbar_wait(accum_full, 0);
-    if (!acc_ok) atomicExch(&failed, 3);
-  }
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  __syncthreads();  // every role is done; `failed` is final and read alike by all threads
-  const bool good = failed == 0;
-  if (my_chunks > 0 && good) {
-    const int n = n0 + warp * 32 + lane;
-    const float bias = (p.bias && blockIdx.y == 0 && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-#pragma unroll
-    for (int t0 = 0; t0 < NT; t0 += 16) {
-      if (t0 >= p.T) break;  // uniform
-      uint32_t v[16];
-      const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)t0;
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,"
-          "%15}, [%16];"
-          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-            "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-            "=r"(v[14]), "=r"(v[15])
-          : "r"(taddr));
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (n < p.N) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int t = t0 + j;
-          if (t >= p.T) break;
-          const float val = __uint_as_float(v[j]) + bias;
-          const size_t o = (size_t)t * p.N + n;
-          if (p.atomic_add) atomicAdd(reinterpret_cast<float*>(p.out) + o, val);
-          else if (p.out_dtype == LSE_F32) reinterpret_cast<float*>(p.out)[o] = val;
-          else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
+  } else if (my_units > 0 && warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer
+      constexpr uint32_t idesc = instr_desc(BM, NT);
+      int it = 0, seg = 0;
+      while (it < my_units && !failed) {
+        const long long u0 = u_begin + it;
+        const int tile = (int)(u0 / p.chunks);
+        const int seg_units = (int)min((long long)my_units - it, (long long)(tile + 1) * p.chunks - u0);
+        const int b = seg & 1;
+        if (seg >= 2 && !mbar_wait(&acc_empty[b], ((seg >> 1) - 1) & 1)) {
+          failed = 2;
+          break;
         }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + b * ACC_COLS;
+        bool ok = true;
+        for (int j = 0; j < seg_units; ++j, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full[s], (it / STAGES) & 1);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t da = smem_desc(smem_u32(w_tiles + s * W_BYTES));
+          const uint64_t db = smem_desc(smem_u32(a_tiles + s * A_BYTES));
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // 16 k-elements = 32 bytes further along the swizzled row: +2 in the address field
+            umma(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // arrives when the MMAs that read this stage are done
+        }
+        if (!ok) {
+          failed = 3;
+          break;
+        }
+        umma_commit(&acc_full[b]);
+        ++seg;
       }
     }
+    __syncwarp();
+  } else if (my_units > 0 && warp >= 2) {
+    // ---- epilogue: warp w may read TMEM lanes 32*(w%4) .. +31, i.e. accumulator rows of that quarter
+    const int quarter = warp & 3;
+    int it = 0, seg = 0;
+    while (it < my_units && !failed) {
+      const long long u0 = u_begin + it;
+      const int tile = (int)(u0 / p.chunks), kc0 = (int)(u0 - (long long)tile * p.chunks);
+      const int seg_units = (int)min((long long)my_units - it, (long long)(tile + 1) * p.chunks - u0);
+      const int b = seg & 1;
+      if (!mbar_wait(&acc_full[b], (seg >> 1) & 1)) {
+        failed = 4;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool whole = seg_units == p.chunks;
+      const int n = tile * BM + quarter * 32 + lane;
+      const float bias = (p.bias && kc0 == 0 && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll 1
+      for (int t0 = 0; t0 < NT && t0 < p.T; t0 += 16) {
+        uint32_t v[16];
+        const uint32_t taddr = tmem_base + b * ACC_COLS + ((uint32_t)(quarter * 32) << 16) + (uint32_t)t0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,"
+            "%14,%15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+              "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (n < p.N) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int t = t0 + j;
+            if (t >= p.T) break;
+            const float val = __uint_as_float(v[j]) + bias;
+            const size_t o = (size_t)t * p.N + n;
+            if (p.atomic_add) atomicAdd(reinterpret_cast<float*>(p.out) + o, val);
+            else if (!whole) failed = 5;  // a partial sum cannot be stored without atomics
+            else if (p.out_dtype == LSE_F32) reinterpret_cast<float*>(p.out)[o] = val;
+            else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
+          }
+        }
+      }
+      // this accumulator may be overwritten once all four epilogue warps have read it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[b])) : "memory");
+      it += seg_units;
+      ++seg;
+    }
   }
-  if (threadIdx.x == 0 && !good) {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();  // every role is done; `failed` is final
+  if (threadIdx.x == 0 && failed != 0) {
     if (p.error_flag) atomicExch(p.error_flag, 100 + failed);
     // copies that were requested must land before the block's shared memory is given up
     for (int c = max(0, issued - STAGES); c < issued; ++c)
       if (!mbar_wait(&full[c % STAGES], (c / STAGES) & 1)) break;
   }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(TMEM_COLS)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS)
                  : "memory");
   }
 }
@@ -275,9 +336,9 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box
 }
 
 template <int NT, int STAGES>
-static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Params& p, dim3 grid,
+static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Params& p, int grid,
                   cudaStream_t stream) {
-  constexpr int smem = STAGES * (BM * BK * 2 + NT * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  constexpr int smem = STAGES * (BM * BK * 2 + NT * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(skinny_gemm_kernel<NT, STAGES>,
@@ -285,8 +346,19 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Params& p,
       return LSE_LAUNCH_FAILED;
     configured = true;
   }
-  skinny_gemm_kernel<NT, STAGES><<<grid, 128, smem, stream>>>(mw, ma, p);
+  skinny_gemm_kernel<NT, STAGES><<<grid, 192, smem, stream>>>(mw, ma, p);
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 1;
+  }
+  return n;
 }
 
 }  // namespace tc
@@ -297,29 +369,32 @@ using namespace lse;
 extern "C" int lse_gemm_bf16_skinny_max_rows(void) { return 256; }
 
 extern "C" int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out,
-                                    int out_dtype, int atomic_add, int T, int N, int K, int split_k,
+                                    int out_dtype, int atomic_add, int T, int N, int K,
                                     int* error_flag, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return LSE_OK;
-  if (T > 256 || K <= 0 || K % 8 || split_k < 1) return LSE_BAD_ARGUMENT;
+  if (T > 256 || K <= 0 || K % 8) return LSE_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) return LSE_BAD_ARGUMENT;
   if (atomic_add && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
-  const int chunks = (K + tc::BK - 1) / tc::BK;
-  if (split_k > chunks) split_k = chunks;
-  if (split_k > 1 && !atomic_add) return LSE_BAD_ARGUMENT;
   const int nt = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
   CUtensorMap mw, ma;
   if (!tc::make_map(&mw, w, N, K, tc::BM) || !tc::make_map(&ma, a, T, K, nt)) return LSE_LAUNCH_FAILED;
   tc::Params p;
   p.T = T; p.N = N; p.K = K;
-  p.chunks_per_split = (chunks + split_k - 1) / split_k;
+  p.tiles = (N + tc::BM - 1) / tc::BM;
+  p.chunks = (K + tc::BK - 1) / tc::BK;
+  p.whole_tiles = atomic_add ? 0 : 1;
   p.out_dtype = out_dtype; p.atomic_add = atomic_add; p.out = out;
   p.bias = reinterpret_cast<const bf16*>(bias); p.error_flag = error_flag;
-  dim3 grid((N + tc::BM - 1) / tc::BM, (chunks + p.chunks_per_split - 1) / p.chunks_per_split);
-  // four stages leave room for several blocks per SM, which hides each block's start and end
+  const long long units = (long long)p.tiles * p.chunks;
+  // two blocks per SM (five stages each fit twice in shared memory) keep more copies in flight
+  const int per_sm = nt <= 32 ? 2 : 1;
+  int grid = tc::sm_count() * per_sm;
+  if (p.whole_tiles) grid = grid < p.tiles ? grid : p.tiles;
+  else if (units < grid) grid = (int)units;
   switch (nt) {
-    case 16: return tc::launch<16, 4>(mw, ma, p, grid, stream);
-    case 32: return tc::launch<32, 4>(mw, ma, p, grid, stream);
-    case 64: return tc::launch<64, 4>(mw, ma, p, grid, stream);
+    case 16: return tc::launch<16, 5>(mw, ma, p, grid, stream);
+    case 32: return tc::launch<32, 5>(mw, ma, p, grid, stream);
+    case 64: return tc::launch<64, 8>(mw, ma, p, grid, stream);
     case 128: return tc::launch<128, 6>(mw, ma, p, grid, stream);
     default: return tc::launch<256, 4>(mw, ma, p, grid, stream);
   }

@@ -25,17 +25,20 @@ int lse_add_rmsnorm(float* x, const void* residual, int residual_dtype, const fl
                     float eps, void* out, int out_dtype, const int* rows, int T, int H,
                     cudaStream_t stream);
 
-// Rotate q and k heads of the fused projection in place (q only is kept there) and write this
-// step's k and v rows into their pages.
-//   qkv [T, (nq + 2 nk) D]; cos/sin float32 [max_pos, D/2] or nullptr for no rotation;
-//   k_pages/v_pages [pages, nk, page_tokens, D] or nullptr when this layer only reads a cache.
-int lse_rope_kv_write(void* qkv, int dtype, int T, int nq, int nk, int D, const int* positions,
-                      const int* token_seq, const float* cos, const float* sin, void* k_pages,
-                      void* v_pages, const int* block_tables, int table_stride, int page_tokens,
-                      cudaStream_t stream);
+// Rotate the q and k heads of the fused projection and write this step's k and v rows into their
+// pages. qkv [T, (nq + 2 nk) D] of in_dtype; the rotated queries go to q_out as `dtype`:
+//   in_dtype == dtype: q_out must be qkv itself (rotated in place, row stride (nq + 2 nk) D);
+//   in_dtype == LSE_F32, dtype == LSE_BF16: q_out is a separate [T, nq D] buffer.
+//   cos/sin float32 [max_pos, D/2] or nullptr for no rotation;
+//   k_pages/v_pages [pages, nk, page_tokens, D] of `dtype`, or nullptr when this layer only reads.
+int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int dtype, int T, int nq, int nk,
+                      int D, const int* positions, const int* token_seq, const float* cos,
+                      const float* sin, void* k_pages, void* v_pages, const int* block_tables,
+                      int table_stride, int page_tokens, cudaStream_t stream);
 
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i]               gu [T, 2I], out [T, I]
-int lse_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream);
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i]     gu [T, 2I] of in_dtype, out [T, I] of dtype
+// (in_dtype == dtype, or float32 in and bfloat16 out)
+int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I, cudaStream_t stream);
 
 // True float32 matrix product: out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]). Each output element is
 // accumulated over k in ascending order by one thread, so a row's result does not depend on T.
@@ -45,12 +48,11 @@ int lse_gemm_f32(const float* a, const float* w, const float* bias, float* out, 
 // bfloat16 product for few rows on tcgen05 tensor cores fed by TMA (gemm_bf16_tc.cu):
 //   out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]),  T <= lse_gemm_bf16_skinny_max_rows(), K % 8 == 0.
 // out_dtype LSE_F32 or LSE_BF16. With atomic_add = 1 (out float32) results are added to what out
-// holds, and K may be split over split_k blocks. error_flag (device-visible int, may be null)
+// holds and the work is balanced over all SMs whatever N is. error_flag (device-visible int, may be null)
 // receives a non-zero code if a bounded wait inside the kernel ran out.
 int lse_gemm_bf16_skinny_max_rows(void);
 int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out, int out_dtype,
-                         int atomic_add, int T, int N, int K, int split_k, int* error_flag,
-                         cudaStream_t stream);
+                         int atomic_add, int T, int N, int K, int* error_flag, cudaStream_t stream);
 
 // Sampling. One token per row of logits [R, V] (float32, row stride V).
 //   temperature[r] < 1e-5 selects the largest logit (lowest index on ties). Otherwise the row is

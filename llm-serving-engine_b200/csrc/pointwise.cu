@@ -4,6 +4,8 @@
 //
 // What each computes follows the reference's fused CPU ops
 // (src/llmserve/kernels/csrc/fused_ops.cpp:39-125) and src/llmserve/attention.py:221-228.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -178,8 +180,11 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int nq, int nk, int D,
 // Same work, 16 bytes at a time: an item is (head, chunk) where the chunk covers kVec elements of
 // the first half of the head and the matching kVec elements of the second half. Needs D/2 to be a
 // multiple of kVec.
-template <typename T>
-__global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nq, int nk, int D,
+// TIn is the type of the fused projection (T itself, or float when the matrix product left float32
+// sums); q_out receives the rotated queries as T (it may alias qkv when TIn == T).
+template <typename TIn, typename T>
+__global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
+                                         int nq, int nk, int D,
                                          const int* __restrict__ positions,
                                          const int* __restrict__ token_seq,
                                          const float* __restrict__ cos_t,
@@ -187,11 +192,12 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nq, int nk, in
                                          T* __restrict__ v_pages,
                                          const int* __restrict__ block_tables, int table_stride,
                                          int page_tokens, int page_shift) {
-  constexpr int V = Num<T>::kVec;
+  constexpr int V = 4;  // elements per item and half
   const int t = blockIdx.x;
   const int half = D >> 1, chunks = half / V;
   const int pos = positions[t];
-  T* row = qkv + (size_t)t * (nq + 2 * nk) * D;
+  const TIn* row = qkv + (size_t)t * (nq + 2 * nk) * D;
+  T* qrow = q_out + (size_t)t * (std::is_same<TIn, T>::value ? (nq + 2 * nk) : nq) * D;
   size_t page_base = 0;
   if (k_pages) {
     int pi, off;
@@ -204,52 +210,55 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, int nq, int nk, in
   const int n_items = ((nq + nk) + (k_pages ? nk : 0)) * chunks;
   for (int it = threadIdx.x; it < n_items; it += blockDim.x) {
     const int head = it / chunks, i = (it - head * chunks) * V;
-    T* h = row + (size_t)head * D;
-    Vec16<T> a = load16(h + i), b = load16(h + i + half);
+    const TIn* h = row + (size_t)head * D;
+    float a[4], b[4];
+    load4<TIn>(h + i, a);
+    load4<TIn>(h + i + half, b);
     if (head < nq + nk && c) {
+      float cv[4], sv[4];
+      load4<float>(c + i, cv);
+      load4<float>(s + i, sv);
 #pragma unroll
       for (int e = 0; e < V; ++e) {
-        const float x1 = Num<T>::to_float(a.v[e]), x2 = Num<T>::to_float(b.v[e]);
-        const float cv = c[i + e], sv = s[i + e];
-        a.v[e] = Num<T>::from_float(x1 * cv - x2 * sv);
-        b.v[e] = Num<T>::from_float(x2 * cv + x1 * sv);
+        const float x1 = a[e], x2 = b[e];
+        a[e] = x1 * cv[e] - x2 * sv[e];
+        b[e] = x2 * cv[e] + x1 * sv[e];
       }
     }
     if (head < nq) {
-      store16(h + i, a);
-      store16(h + i + half, b);
+      T* dst = qrow + (size_t)head * D;
+      store4<T>(dst + i, a);
+      store4<T>(dst + i + half, b);
     } else if (k_pages) {
       const bool is_k = head < nq + nk;
       const int kvh = is_k ? head - nq : head - nq - nk;
       T* dst = (is_k ? k_pages : v_pages) + page_base + (size_t)kvh * page_tokens * D;
-      store16(dst + i, a);
-      store16(dst + i + half, b);
+      store4<T>(dst + i, a);
+      store4<T>(dst + i + half, b);
     }
   }
 }
 
 // ------------------------------------------------------------------------------------ silu * up
-template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I) {
+template <typename TIn, typename T>
+__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I) {
   const size_t t = blockIdx.x;
-  const T* g = gu + t * 2 * I;
-  const T* u = g + I;
+  const TIn* g = gu + t * 2 * I;
+  const TIn* u = g + I;
   T* o = out + t * I;
-  constexpr int V = Num<T>::kVec;
-  if (I % V == 0) {
-    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * V; i < I; i += gridDim.y * blockDim.x * V) {
-      Vec16<T> gv = load16(g + i), uv = load16(u + i), ov;
+  if (I % 4 == 0) {
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < I; i += gridDim.y * blockDim.x * 4) {
+      float gv[4], uv[4];
+      load4<TIn>(g + i, gv);
+      load4<TIn>(u + i, uv);
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        const float a = Num<T>::to_float(gv.v[j]);
-        ov.v[j] = Num<T>::from_float(a / (1.f + expf(-a)) * Num<T>::to_float(uv.v[j]));
-      }
-      store16(o + i, ov);
+      for (int j = 0; j < 4; ++j) gv[j] = gv[j] / (1.f + expf(-gv[j])) * uv[j];
+      store4<T>(o + i, gv);
     }
   } else {
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
-      const float a = Num<T>::to_float(g[i]);
-      o[i] = Num<T>::from_float(a / (1.f + expf(-a)) * Num<T>::to_float(u[i]));
+      const float a = Num<TIn>::to_float(g[i]);
+      o[i] = Num<T>::from_float(a / (1.f + expf(-a)) * Num<TIn>::to_float(u[i]));
     }
   }
 }
@@ -303,48 +312,54 @@ extern "C" int lse_add_rmsnorm(float* x, const void* residual, int residual_dtyp
   return LSE_CHECK_LAUNCH();
 }
 
-extern "C" int lse_rope_kv_write(void* qkv, int dtype, int T, int nq, int nk, int D,
-                                 const int* positions, const int* token_seq, const float* cos,
-                                 const float* sin, void* k_pages, void* v_pages,
+extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int dtype, int T, int nq,
+                                 int nk, int D, const int* positions, const int* token_seq,
+                                 const float* cos, const float* sin, void* k_pages, void* v_pages,
                                  const int* block_tables, int table_stride, int page_tokens,
                                  cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
   if (D % 2 || page_tokens <= 0 || (cos == nullptr) != (sin == nullptr) ||
       (k_pages == nullptr) != (v_pages == nullptr))
     return LSE_BAD_ARGUMENT;
+  if (in_dtype != dtype && in_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
+  if (in_dtype == dtype && q_out != qkv) return LSE_BAD_ARGUMENT;  // same type: rotated in place
   const int ps = shift_of(page_tokens);
-  const bool vec = (D / 2) % (dtype == LSE_F32 ? 4 : 8) == 0;
-  if (vec && dtype == LSE_F32)
-    rope_kv_write_vec_kernel<float><<<T, 256, 0, stream>>>(
-        (float*)qkv, nq, nk, D, positions, token_seq, cos, sin, (float*)k_pages, (float*)v_pages,
-        block_tables, table_stride, page_tokens, ps);
-  else if (vec && dtype == LSE_BF16)
-    rope_kv_write_vec_kernel<bf16><<<T, 256, 0, stream>>>(
-        (bf16*)qkv, nq, nk, D, positions, token_seq, cos, sin, (bf16*)k_pages, (bf16*)v_pages,
-        block_tables, table_stride, page_tokens, ps);
+  const bool vec = (D / 2) % 4 == 0;
+#define LSE_ROPE_VEC(TIn, T)                                                                      \
+  rope_kv_write_vec_kernel<TIn, T><<<T_, 256, 0, stream>>>(                                       \
+      (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,         \
+      (T*)v_pages, block_tables, table_stride, page_tokens, ps)
+  const int T_ = T;
+  if (vec && in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ROPE_VEC(float, float);
+  else if (vec && in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ROPE_VEC(bf16, bf16);
+  else if (vec && in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_ROPE_VEC(float, bf16);
+  else if (in_dtype != dtype) return LSE_BAD_ARGUMENT;
   else if (dtype == LSE_F32)
     rope_kv_write_kernel<float><<<T, 256, 0, stream>>>(
-        (float*)qkv, nq, nk, D, positions, token_seq, cos, sin, (float*)k_pages, (float*)v_pages,
+        (float*)q_out, nq, nk, D, positions, token_seq, cos, sin, (float*)k_pages, (float*)v_pages,
         block_tables, table_stride, page_tokens, ps);
   else if (dtype == LSE_BF16)
     rope_kv_write_kernel<bf16><<<T, 256, 0, stream>>>(
-        (bf16*)qkv, nq, nk, D, positions, token_seq, cos, sin, (bf16*)k_pages, (bf16*)v_pages,
+        (bf16*)q_out, nq, nk, D, positions, token_seq, cos, sin, (bf16*)k_pages, (bf16*)v_pages,
         block_tables, table_stride, page_tokens, ps);
   else
     return LSE_BAD_ARGUMENT;
+#undef LSE_ROPE_VEC
   return LSE_CHECK_LAUNCH();
 }
 
-extern "C" int lse_silu_mul(const void* gu, void* out, int dtype, int T, int I,
+extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I,
                             cudaStream_t stream) {
   if (T <= 0 || I <= 0) return LSE_OK;
   const int threads = 256;
-  const int per_block = threads * (dtype == LSE_F32 ? 4 : 8);
+  const int per_block = threads * 4;
   dim3 grid(T, min((I + per_block - 1) / per_block, 65535));
-  if (dtype == LSE_F32)
-    silu_mul_kernel<float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
-  else if (dtype == LSE_BF16)
-    silu_mul_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+  if (in_dtype == LSE_F32 && dtype == LSE_F32)
+    silu_mul_kernel<float, float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
+  else if (in_dtype == LSE_BF16 && dtype == LSE_BF16)
+    silu_mul_kernel<bf16, bf16><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+  else if (in_dtype == LSE_F32 && dtype == LSE_BF16)
+    silu_mul_kernel<float, bf16><<<grid, threads, 0, stream>>>((const float*)gu, (bf16*)out, I);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();

@@ -34,6 +34,7 @@ class CudaOps:
         self.force_simt_attention = False
         self.use_skinny_gemm = True
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
+        self.skinny_atomic_rows = 64  # above this the atomics' traffic is no longer small
         self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
 
     # ------------------------------------------------------------------ capabilities
@@ -78,38 +79,46 @@ class CudaOps:
         self.launches += 1
         return out
 
-    def silu_mul(self, gu):
-        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=gu.dtype, device=gu.device)
+    def silu_mul(self, gu, out_dtype=None):
+        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=out_dtype or gu.dtype, device=gu.device)
         self.ext.silu_mul(gu, out)
         self.launches += 1
         return out
 
     # ------------------------------------------------------------------ matrix products
-    def linear(self, a, w, bias=None, out_dtype=None):
-        out_dtype = out_dtype or a.dtype
+    def linear(self, a, w, bias=None, out_dtype=None, accumulate_into=None):
+        """``a @ w.T (+ bias)``.
+
+        out_dtype None asks for "an activation for the next kernel of this package": the compute
+        dtype, or float32 sums where those come for free (the kernels that read activations take
+        both). With ``accumulate_into`` (a float32 tensor of the result's shape) the product may be
+        added into that tensor instead; the return value is then None.
+        """
         if a.dtype == torch.float32:
             if w.dtype != torch.float32:
                 raise TypeError("float32 activations need float32 weights")
             out = torch.empty(a.shape[0], w.shape[0], dtype=torch.float32, device=a.device)
             self.ext.gemm_f32(a, w, bias, out)
             self.launches += 1
-            return out if out_dtype == torch.float32 else out.to(out_dtype)
+            return out if out_dtype in (None, torch.float32) else out.to(out_dtype)
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise TypeError(f"linear: unsupported dtypes {a.dtype} x {w.dtype}")
         T, K = a.shape
         N = w.shape[0]
-        if (self.use_skinny_gemm and T <= self.skinny_max_rows and K % 8 == 0
-                and out_dtype == torch.float32):
-            # few rows: stream the weights once through the tcgen05 kernel
-            tiles, chunks = -(-N // 128), -(-K // 64)
-            split = 1
-            if out_dtype == torch.float32:
-                split = max(1, min(2 * self.num_sms // tiles, chunks // 4))
-            if split > 1:
-                out = torch.zeros(T, N, dtype=torch.float32, device=a.device)
-            else:
-                out = torch.empty(T, N, dtype=out_dtype, device=a.device)
-            self.ext.gemm_bf16_skinny(a, w, bias, out, split > 1, split)
+        if self.use_skinny_gemm and T <= self.skinny_atomic_rows and K % 8 == 0:
+            # few rows: the weights are streamed once through the tcgen05 kernel, work balanced
+            # over all SMs, float32 sums added with atomics
+            if out_dtype == torch.bfloat16:
+                out = torch.empty(T, N, dtype=torch.bfloat16, device=a.device)
+                self.ext.gemm_bf16_skinny(a, w, bias, out, False)
+                self.launches += 1
+                return out
+            if accumulate_into is not None:
+                self.ext.gemm_bf16_skinny(a, w, bias, accumulate_into, True)
+                self.launches += 1
+                return None
+            out = torch.zeros(T, N, dtype=torch.float32, device=a.device)
+            self.ext.gemm_bf16_skinny(a, w, bias, out, True)
             self.launches += 1
             return out
         if out_dtype == torch.float32:
@@ -123,10 +132,13 @@ class CudaOps:
 
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
-                      cos, sin, k_pages, v_pages, block_tables, page_tokens):
-        self.ext.rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, positions, token_seq,
-                               cos, sin, k_pages, v_pages, block_tables, page_tokens)
+                      cos, sin, k_pages, v_pages, block_tables, page_tokens, out_dtype):
+        """Rotate q and k, write k and v into their pages; returns the rotated queries."""
+        q = self.ext.rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, positions, token_seq,
+                                   cos, sin, k_pages, v_pages, block_tables, page_tokens,
+                                   out_dtype == torch.bfloat16)
         self.launches += 1
+        return q
 
     def attention_q_tile(self, dtype, head_dim):
         return int(self.ext.attention_q_tile(head_dim, dtype == torch.bfloat16,
@@ -156,9 +168,9 @@ class CudaOps:
         want = max(1, (6 * self.num_sms + blocks - 1) // blocks)
         return int(max(1, min(want, (max_ctx + 63) // 64, 64)))
 
-    def paged_attention(self, qkv, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
+    def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan):
-        out = torch.empty(qkv.shape[0], num_heads * head_dim, dtype=qkv.dtype, device=qkv.device)
+        out = torch.empty(q.shape[0], num_heads * head_dim, dtype=q.dtype, device=q.device)
         n_tiles = int(plan["tiles"].shape[0])
         n_dec = int(plan["decode_seqs"].shape[0])
         splits = step.decode_splits if step.decode_splits else self.decode_splits(
@@ -168,7 +180,7 @@ class CudaOps:
             self.reserve_attention_scratch(head_dim, n_dec, num_heads, splits)
             scratch = self._scratch
         self.ext.paged_attention(
-            qkv, out, k_pages, v_pages, num_heads, num_kv_heads, head_dim, float(scale),
+            q, out, k_pages, v_pages, num_heads, num_kv_heads, head_dim, float(scale),
             int(window), block_tables, step.ctx_lens, step.cu_q,
             plan["tiles"] if n_tiles else None, n_tiles,
             plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,

@@ -81,13 +81,15 @@ class PagedAttention(Mixer):
     def plan_step(self, host_step, group):
         return self.ops.attention_plan(host_step, self.env.dtype, self.spec.head_dim)
 
-    def forward(self, h, step, cache):
+    accepts_residual = True
+
+    def forward(self, h, step, cache, residual=None):
         s = self.spec
         ops = self.ops
-        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias, out_dtype=self.env.dtype)
+        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias)
         tables = step.block_tables[cache.group]
         cos, sin = self.rotary if self.rotary is not None else (None, None)
-        ops.rope_kv_write(
+        q = ops.rope_kv_write(
             qkv,
             num_heads=s.num_heads,
             num_kv_heads=s.num_kv_heads,
@@ -100,9 +102,10 @@ class PagedAttention(Mixer):
             v_pages=cache.v if cache.writes else None,
             block_tables=tables,
             page_tokens=cache.page_tokens,
+            out_dtype=self.env.dtype,
         )
         o = ops.paged_attention(
-            qkv,
+            q,
             num_heads=s.num_heads,
             num_kv_heads=s.num_kv_heads,
             head_dim=s.head_dim,
@@ -115,4 +118,5 @@ class PagedAttention(Mixer):
             step=step,
             plan=step.plans[self.plan_key()],
         )
-        return ops.linear(o, self.o_weight, self.o_bias, out_dtype=self.env.residual_dtype)
+        return ops.linear(o, self.o_weight, self.o_bias, out_dtype=self.env.residual_dtype,
+                          accumulate_into=residual)

@@ -148,6 +148,10 @@ class Mixer(Part):
     of the cache layer this run of the layer is bound to; ``cache.writes`` is False when the layer
     only reads a cache that an earlier layer filled.
 
+    A mixer (or feed-forward) class with ``accepts_residual = True`` is also handed the float32
+    residual stream as ``residual=x``; it may add its result into it and return None instead of
+    returning the result.
+
     ``cache_need()`` says what the mixer keeps per request (None for nothing).
     ``plan_step(host_step, group) -> dict[str, np.ndarray]`` may return int32 work lists that are
     the same for every layer with the same ``plan_key()``; the runner uploads them once per step

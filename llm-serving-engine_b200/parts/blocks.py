@@ -42,6 +42,11 @@ class PreNormBlock(Block):
 
     def forward(self, x, pending, step, cache):
         h = self.norm_in.forward(x, pending)
-        a = self.mixer.forward(h, step, cache)
+        if getattr(self.mixer, "accepts_residual", False):
+            a = self.mixer.forward(h, step, cache, residual=x)  # None: already added into x
+        else:
+            a = self.mixer.forward(h, step, cache)
         h = self.norm_post.forward(x, a)
+        if getattr(self.feed_forward, "accepts_residual", False):
+            return x, self.feed_forward.forward(h, step, residual=x)
         return x, self.feed_forward.forward(h, step)

@@ -33,8 +33,11 @@ class SwiGLU(FeedForward):
         self.gate_up_weight = params["gate_up.weight"]
         self.down_weight = params["down.weight"]
 
-    def forward(self, h, step):
+    accepts_residual = True
+
+    def forward(self, h, step, residual=None):
         ops = self.ops
-        gu = ops.linear(h, self.gate_up_weight, None, out_dtype=self.env.dtype)
-        a = ops.silu_mul(gu)
-        return ops.linear(a, self.down_weight, None, out_dtype=self.env.residual_dtype)
+        gu = ops.linear(h, self.gate_up_weight, None)
+        a = ops.silu_mul(gu, out_dtype=self.env.dtype)
+        return ops.linear(a, self.down_weight, None, out_dtype=self.env.residual_dtype,
+                          accumulate_into=residual)

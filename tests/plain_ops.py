@@ -35,6 +35,7 @@ class PlainOps:
     def __init__(self, q_tile: int = 32) -> None:
         self.q_tile = q_tile
         self.launches = 0
+        self.accumulate = True  # add into the residual stream where a part offers it
 
     # ------------------------------------------------------------------ capabilities
     def branch_dtype(self, dtype):
@@ -60,20 +61,24 @@ class PlainOps:
         y = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight
         return y.to(out_dtype)
 
-    def silu_mul(self, gu):
+    def silu_mul(self, gu, out_dtype=None):
         g, u = gu.float().chunk(2, dim=-1)
-        return (g / (1 + torch.exp(-g)) * u).to(gu.dtype)
+        return (g / (1 + torch.exp(-g)) * u).to(out_dtype or gu.dtype)
 
-    def linear(self, a, w, bias=None, out_dtype=None):
+    def linear(self, a, w, bias=None, out_dtype=None, accumulate_into=None):
         y = a.float() @ w.float().T
         if bias is not None:
             y = y + bias.float()
+        if accumulate_into is not None and self.accumulate:
+            accumulate_into += y
+            return None
         return y.to(out_dtype or a.dtype)
 
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
-                      cos, sin, k_pages, v_pages, block_tables, page_tokens):
+                      cos, sin, k_pages, v_pages, block_tables, page_tokens, out_dtype=None):
         T, D = qkv.shape[0], head_dim
+        out_dtype = out_dtype or qkv.dtype
         heads = qkv.view(T, num_heads + 2 * num_kv_heads, D)
         pos = positions.long()
         rot = heads[:, : num_heads + num_kv_heads].float()
@@ -81,12 +86,15 @@ class PlainOps:
             c, s = cos[pos][:, None, :], sin[pos][:, None, :]
             x1, x2 = rot[..., : D // 2], rot[..., D // 2 :]
             rot = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
-        heads[:, :num_heads] = rot[:, :num_heads].to(qkv.dtype)
         if k_pages is not None:
             page = block_tables[token_seq.long(), pos // page_tokens].long()
             off = pos % page_tokens
-            k_pages[page, :, off] = rot[:, num_heads:].to(qkv.dtype)
-            v_pages[page, :, off] = heads[:, num_heads + num_kv_heads :]
+            k_pages[page, :, off] = rot[:, num_heads:].to(out_dtype)
+            v_pages[page, :, off] = heads[:, num_heads + num_kv_heads :].to(out_dtype)
+        if out_dtype == qkv.dtype:
+            heads[:, :num_heads] = rot[:, :num_heads].to(qkv.dtype)
+            return qkv[:, : num_heads * D]
+        return rot[:, :num_heads].to(out_dtype).reshape(T, num_heads * D)
 
     def attention_plan(self, host_step, dtype, head_dim):
         tiles, decode = [], []
@@ -100,10 +108,11 @@ class PlainOps:
             "decode_seqs": np.asarray(decode, dtype=np.int32),
         }
 
-    def paged_attention(self, qkv, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
+    def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan=None):
-        T, D = qkv.shape[0], head_dim
-        q = qkv[:, : num_heads * D].float().view(T, num_heads, D)
+        T, D = q.shape[0], head_dim
+        qkv = q
+        q = q[:, : num_heads * D].float().reshape(T, num_heads, D)
         out = torch.zeros(T, num_heads, D)
         cu = step.cu_q.tolist()
         ctx = step.ctx_lens.tolist()

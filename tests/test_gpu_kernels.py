@@ -102,6 +102,42 @@ def test_linear_bf16(ops, T, N, K, bias):
     ops.check_kernel_errors()
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 2048, 2048), (8, 200, 8192), (33, 6144, 520), (64, 130, 64)])
+def test_linear_bf16_adds_into_the_residual_stream(ops, T, N, K):
+    a, w = rnd(T, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, seed=2, scale=0.05)
+    x = rnd(T, N, seed=5)
+    xg = x.clone().cuda()
+    assert ops.linear(a.cuda(), w.cuda(), None, out_dtype=torch.float32, accumulate_into=xg) is None
+    ref = x.double() + a.double() @ w.double().T
+    assert (xg.double().cpu() - ref).abs().max() <= 3e-6 * K**0.5 * ref.abs().max()
+    ops.check_kernel_errors()
+
+
+def test_pointwise_kernels_read_float32_sums(ops):
+    """Activations may reach rope and the SiLU gate as float32 sums and leave as bfloat16."""
+    gu = rnd(5, 2 * 104, seed=1, scale=2.0)
+    got = ops.silu_mul(gu.cuda(), out_dtype=torch.bfloat16)
+    assert got.dtype == torch.bfloat16
+    close(got, PlainOps().silu_mul(gu), "bfloat16", rel16=0.005)
+    nq, nk, D, page = 6, 2, 48, 8
+    case = paged_case(3, [1, 20, 2], [30, 20, 9], nq, nk, D, page, torch.bfloat16, seed=2)
+    qkv, kp, vp, tables, positions, token_seq, step = case
+    qkv32 = rnd(qkv.shape[0], qkv.shape[1], seed=3)
+    ang = torch.outer(torch.arange(64, dtype=torch.float64), 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float64) / D)))
+    cos, sin = ang.cos().float(), ang.sin().float()
+    kw = dict(num_heads=nq, num_kv_heads=nk, head_dim=D, positions=positions, token_seq=token_seq,
+              block_tables=tables, page_tokens=page, out_dtype=torch.bfloat16)
+    kp_ref, vp_ref = kp.clone(), vp.clone()
+    q_ref = PlainOps().rope_kv_write(qkv32.clone(), cos=cos, sin=sin, k_pages=kp_ref, v_pages=vp_ref, **kw)
+    kp_g, vp_g = kp.cuda(), vp.cuda()
+    gkw = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in kw.items()}
+    q_g = ops.rope_kv_write(qkv32.cuda(), cos=cos.cuda(), sin=sin.cuda(), k_pages=kp_g, v_pages=vp_g, **gkw)
+    assert q_g.dtype == torch.bfloat16 and q_g.shape == (qkv.shape[0], nq * D)
+    close(q_g, q_ref, "bfloat16", rel16=0.005)
+    close(kp_g, kp_ref, "bfloat16", rel16=0.005)
+    close(vp_g, vp_ref, "bfloat16", rel16=0.005)
+
+
 def test_skinny_gemm_sees_every_k_and_every_row(ops):
     """One-hot inputs: a wrong swizzle, k offset or row mapping shows up as a misplaced value."""
     T, N, K = 5, 300, 328
@@ -155,15 +191,16 @@ def run_attention(ops, case, nq, nk, D, page, window, max_pos, theta=10000.0, sp
     plain = PlainOps()
     q_ref, kp_ref, vp_ref = qkv.clone(), kp.clone(), vp.clone()
     kw = dict(num_heads=nq, num_kv_heads=nk, head_dim=D)
-    plain.rope_kv_write(q_ref, **kw, positions=positions, token_seq=token_seq, cos=cos, sin=sin,
-                        k_pages=kp_ref, v_pages=vp_ref, block_tables=tables, page_tokens=page)
+    q_ref = plain.rope_kv_write(q_ref, **kw, positions=positions, token_seq=token_seq, cos=cos, sin=sin,
+                                k_pages=kp_ref, v_pages=vp_ref, block_tables=tables, page_tokens=page)
     ref = plain.paged_attention(q_ref, **kw, scale=scale, window=window, k_pages=kp_ref,
                                 v_pages=vp_ref, block_tables=tables, page_tokens=page, step=step)
     dev = lambda t: None if t is None else t.cuda()
     ops.check_attention_shape(D, qkv.dtype)
     q_g, kp_g, vp_g = qkv.cuda(), kp.cuda(), vp.cuda()
-    ops.rope_kv_write(q_g, **kw, positions=dev(positions), token_seq=dev(token_seq), cos=dev(cos),
-                      sin=dev(sin), k_pages=kp_g, v_pages=vp_g, block_tables=dev(tables), page_tokens=page)
+    q_g = ops.rope_kv_write(q_g, **kw, positions=dev(positions), token_seq=dev(token_seq), cos=dev(cos),
+                            sin=dev(sin), k_pages=kp_g, v_pages=vp_g, block_tables=dev(tables),
+                            page_tokens=page, out_dtype=qkv.dtype)
     gstep = SimpleNamespace(cu_q=step.cu_q.cuda(), ctx_lens=step.ctx_lens.cuda(), decode_splits=splits,
                             max_decode_ctx=step.max_decode_ctx)
     plan = {k: torch.from_numpy(v).cuda() for k, v in ops.attention_plan(step, qkv.dtype, D).items()}

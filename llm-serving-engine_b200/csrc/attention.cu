@@ -619,6 +619,42 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
+// ---- no-allocation variant: scratch inside the library's device image ---------------------------
+// In host code the array's name is only a handle for the runtime, not a device address; the
+// address each device gives it is looked up once per device with cudaGetSymbolAddress.
+static __device__ __align__(256) float g_noalloc_scratch[LSE_ATTN_NOALLOC_MAX_FLOATS];
+
+static float* noalloc_scratch_address() {
+  constexpr int kMaxDevices = 64;
+  static float* address[kMaxDevices] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!address[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess) {
+      cudaGetLastError();  // leave no sticky error behind
+      return nullptr;
+    }
+    address[dev] = static_cast<float*>(p);
+  }
+  return address[dev];
+}
+
+extern "C" size_t lse_attn_decode_noalloc_max_floats(void) { return LSE_ATTN_NOALLOC_MAX_FLOATS; }
+
+extern "C" int lse_attn_decode_noalloc(const LseAttnArgs* a, cudaStream_t stream) {
+  if (!args_ok(a) || (a->num_decode > 0 && !a->decode_seqs)) return LSE_BAD_ARGUMENT;
+  if (a->num_decode <= 0) return LSE_OK;
+  if (a->num_splits < 1) return LSE_BAD_ARGUMENT;
+  if (lse_attn_decode_scratch_floats(a->num_decode, a->num_heads, a->num_splits) >
+      (size_t)LSE_ATTN_NOALLOC_MAX_FLOATS)
+    return LSE_TOO_LARGE;
+  LseAttnArgs b = *a;
+  b.scratch = noalloc_scratch_address();
+  if (!b.scratch) return LSE_LAUNCH_FAILED;
+  return b.dtype == LSE_F32 ? launch_decode<float>(&b, stream) : launch_decode<bf16>(&b, stream);
+}
+
 extern "C" int lse_attn_decode(const LseAttnArgs* a, cudaStream_t stream) {
   if (!args_ok(a) || (a->num_decode > 0 && !a->decode_seqs)) return LSE_BAD_ARGUMENT;
   if (a->num_decode <= 0) return LSE_OK;

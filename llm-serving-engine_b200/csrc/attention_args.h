@@ -41,4 +41,29 @@ int lse_attn_q_tile(int dtype);
 size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, int num_splits);
 int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream);
 int lse_attn_decode(const LseAttnArgs* a, cudaStream_t stream);
+
+// ---- Single-token attention for callers that cannot allocate device memory ---------------------
+// (This entry point has no counterpart in the reference, whose attention runs on the CPU.)
+//
+// lse_attn_decode needs a scratch buffer for the partial results of its context partitions, and
+// the caller has to allocate it. Some callers cannot: a host program that has given all device
+// memory to its own pool and may not call cudaMalloc any more, or a latency-critical serving loop
+// that must never meet cudaMalloc's implicit device-wide synchronisation. For them lse_attn_decode_noalloc does the same computation with the scratch in
+// a buffer that is part of this library's device image: LSE_ATTN_NOALLOC_MAX_FLOATS floats (4 MiB),
+// held on every GPU that loads the library until the process exits. The caller still passes the
+// inputs and the output; `a->scratch` is ignored. The function calls no cudaMalloc, cudaFree or
+// other allocating routine.
+//
+//  * Size limit: num_decode * num_heads * num_splits * (D + 2) must not exceed
+//    LSE_ATTN_NOALLOC_MAX_FLOATS when num_splits > 1; otherwise nothing is launched and
+//    LSE_TOO_LARGE is returned (lse_attn_decode_noalloc_max_floats() reports the limit).
+//  * First call on a device: it looks up the buffer's device address (cudaGetSymbolAddress, with
+//    that device current) and remembers it. Make that first call outside any stream capture.
+//  * The buffer is shared by every call and keeps the last call's contents. Nothing in it has to
+//    start at zero: each launch writes every partial result it later reads. Two calls whose
+//    kernels overlap on the GPU (different streams) would race on it; run them one after the other.
+#define LSE_ATTN_NOALLOC_MAX_FLOATS (1 << 20)
+#define LSE_TOO_LARGE 3
+size_t lse_attn_decode_noalloc_max_floats(void);
+int lse_attn_decode_noalloc(const LseAttnArgs* a, cudaStream_t stream);
 }

@@ -365,6 +365,8 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   constexpr int VEC = S::VEC, NCHUNK = S::NCHUNK, LPK = S::LPK, CPL = S::CPL, KPI = S::KPI;
   __shared__ float sm_m[DEC_WARPS][GT], sm_l[DEC_WARPS][GT];
   __shared__ float sm_acc[DEC_WARPS][GT][D];
+  pdl_trigger();
+  pdl_wait();
 
   const int split = blockIdx.x, b = blockIdx.z;
   const int G = a.num_heads / a.num_kv_heads;
@@ -526,6 +528,8 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
 
 template <typename T>
 __global__ void decode_merge_kernel(const LseAttnArgs a) {
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
   const int seq = a.decode_seqs[b];
   const int tok = a.cu_q[seq];
@@ -566,13 +570,13 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
   dim3 grid(a->num_splits, a->num_kv_heads * ((G + gt - 1) / gt), a->num_decode);
   if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
-  if (gt == 1) decode_split_kernel<T, 1><<<grid, DEC_WARPS * 32, 0, stream>>>(*a, ps);
-  else if (gt == 2) decode_split_kernel<T, 2><<<grid, DEC_WARPS * 32, 0, stream>>>(*a, ps);
-  else decode_split_kernel<T, 4><<<grid, DEC_WARPS * 32, 0, stream>>>(*a, ps);
+  if (gt == 1) launch(decode_split_kernel<T, 1>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
+  else if (gt == 2) launch(decode_split_kernel<T, 2>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
+  else launch(decode_split_kernel<T, 4>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   if (cudaGetLastError() != cudaSuccess) return LSE_LAUNCH_FAILED;
   if (a->num_splits > 1) {
     dim3 mgrid(a->num_decode, a->num_heads);
-    decode_merge_kernel<T><<<mgrid, D < 32 ? 32 : (D > 128 ? 128 : D), 0, stream>>>(*a);
+    launch(decode_merge_kernel<T>, mgrid, D < 32 ? 32 : (D > 128 ? 128 : D), 0, stream, *a);
     if (cudaGetLastError() != cudaSuccess) return LSE_LAUNCH_FAILED;
   }
   return LSE_OK;

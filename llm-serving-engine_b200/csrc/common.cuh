@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "status.h"
 
@@ -81,5 +82,37 @@ __device__ __forceinline__ void page_of(int pos, int page_tokens, int page_shift
     off = pos - idx * page_tokens;
   }
 }
+
+// Programmatic dependent launch. A kernel launched through lse::launch may be scheduled while
+// the kernel before it in the stream is still running; it must call pdl_wait() before it touches
+// anything that kernel (or any earlier one) wrote, and may do work that depends on nothing first.
+// pdl_trigger() lets the *next* kernel in the stream be scheduled early in the same way.
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#ifdef __CUDACC__
+inline bool pdl_enabled() {
+  static const bool on = (getenv("LSE_NO_PDL") == nullptr);
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                          cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
 
 }  // namespace lse

@@ -151,6 +151,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   block_range(p, u_begin, u_end);
   const int my_units = (int)(u_end - u_begin);
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -181,17 +182,30 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   // try_wait would take turns with the role lane of its own warp and stall the pipeline.
   if (my_units > 0 && warp == 0) {
     if (lane == 0) {
-      // ---- TMA producer: one (weights, activations) stage per unit
-      for (int it = 0; it < my_units && !failed; ++it) {
-        const int s = it % STAGES;
-        if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
-          failed = 1;
-          break;
-        }
+      // ---- TMA producer: one (weights, activations) stage per unit. The weights depend on no
+      // earlier kernel, so the first STAGES weight tiles are requested before pdl_wait(); the
+      // activations (written by the kernel before this one) only after it.
+      const int early = min(my_units, STAGES);
+      for (int it = 0; it < early; ++it) {
         const long long u = u_begin + it;
         const int tile = (int)(u / p.chunks), kc = (int)(u - (long long)tile * p.chunks);
-        mbar_expect_tx(&full[s], W_BYTES + A_BYTES);
-        tma_load_2d(w_tiles + s * W_BYTES, &map_w, &full[s], kc * BK, tile * BM);
+        mbar_expect_tx(&full[it], W_BYTES + A_BYTES);
+        tma_load_2d(w_tiles + it * W_BYTES, &map_w, &full[it], kc * BK, tile * BM);
+        issued = it + 1;
+      }
+      pdl_wait();
+      for (int it = 0; it < my_units && !failed; ++it) {
+        const int s = it % STAGES;
+        const long long u = u_begin + it;
+        const int tile = (int)(u / p.chunks), kc = (int)(u - (long long)tile * p.chunks);
+        if (it >= STAGES) {
+          if (!mbar_wait(&empty[s], ((it / STAGES) - 1) & 1)) {
+            failed = 1;
+            break;
+          }
+          mbar_expect_tx(&full[s], W_BYTES + A_BYTES);
+          tma_load_2d(w_tiles + s * W_BYTES, &map_w, &full[s], kc * BK, tile * BM);
+        }
         tma_load_2d(a_tiles + s * A_BYTES, &map_a, &full[s], kc * BK, 0);
         issued = it + 1;
       }
@@ -240,6 +254,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else if (my_units > 0 && warp >= 2) {
     // ---- epilogue: warp w may read TMEM lanes 32*(w%4) .. +31, i.e. accumulator rows of that quarter
     const int quarter = warp & 3;
+    pdl_wait();  // the output may still be read or written by the kernels before this one
     int it = 0, seg = 0;
     while (it < my_units && !failed) {
       const long long u0 = u_begin + it;
@@ -346,8 +361,9 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Params& p,
       return LSE_LAUNCH_FAILED;
     configured = true;
   }
-  skinny_gemm_kernel<NT, STAGES><<<grid, 192, smem, stream>>>(mw, ma, p);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return lse::launch(skinny_gemm_kernel<NT, STAGES>, grid, 192, smem, stream, mw, ma, p) == cudaSuccess
+             ? LSE_OK
+             : LSE_LAUNCH_FAILED;
 }
 
 static int sm_count() {

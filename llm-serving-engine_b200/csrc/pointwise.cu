@@ -15,6 +15,8 @@ namespace lse {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const T* src = table + (size_t)ids[t] * H;
   float* dst = out + (size_t)t * H;
@@ -68,6 +70,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TR* __restrict__
                                    const float* __restrict__ weight, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int H) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src_row = rows ? rows[r] : r;
   float* xr = x + (size_t)src_row * H;
@@ -193,6 +197,8 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
                                          const int* __restrict__ block_tables, int table_stride,
                                          int page_tokens, int page_shift) {
   constexpr int V = 4;  // elements per item and half
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = D >> 1, chunks = half / V;
   const int pos = positions[t];
@@ -242,6 +248,8 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
 // ------------------------------------------------------------------------------------ silu * up
 template <typename TIn, typename T>
 __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I) {
+  pdl_trigger();
+  pdl_wait();
   const size_t t = blockIdx.x;
   const TIn* g = gu + t * 2 * I;
   const TIn* u = g + I;
@@ -281,9 +289,9 @@ extern "C" int lse_embedding(const int* ids, const void* table, int table_dtype,
   if (T <= 0) return LSE_OK;
   const int threads = H >= 2048 ? 256 : 128;
   if (table_dtype == LSE_F32)
-    embedding_kernel<float><<<T, threads, 0, stream>>>(ids, (const float*)table, out, H);
+    launch(embedding_kernel<float>, T, threads, 0, stream, ids, (const float*)table, out, H);
   else if (table_dtype == LSE_BF16)
-    embedding_kernel<bf16><<<T, threads, 0, stream>>>(ids, (const bf16*)table, out, H);
+    launch(embedding_kernel<bf16>, T, threads, 0, stream, ids, (const bf16*)table, out, H);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();
@@ -297,11 +305,11 @@ extern "C" int lse_add_rmsnorm(float* x, const void* residual, int residual_dtyp
 #define LSE_NORM(TR, TO)                                                      \
   do {                                                                        \
     if (H % 4 == 0)                                                           \
-      add_rmsnorm_kernel<TR, TO, true><<<T, threads, 0, stream>>>(            \
-          x, (const TR*)residual, weight, eps, (TO*)out, rows, H);            \
+      launch(add_rmsnorm_kernel<TR, TO, true>, T, threads, 0, stream,         \
+             x, (const TR*)residual, weight, eps, (TO*)out, rows, H);         \
     else                                                                      \
-      add_rmsnorm_kernel<TR, TO, false><<<T, threads, 0, stream>>>(           \
-          x, (const TR*)residual, weight, eps, (TO*)out, rows, H);            \
+      launch(add_rmsnorm_kernel<TR, TO, false>, T, threads, 0, stream,        \
+             x, (const TR*)residual, weight, eps, (TO*)out, rows, H);         \
   } while (0)
   if (residual_dtype == LSE_F32 && out_dtype == LSE_F32) LSE_NORM(float, float);
   else if (residual_dtype == LSE_F32 && out_dtype == LSE_BF16) LSE_NORM(float, bf16);
@@ -326,9 +334,9 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
   const int ps = shift_of(page_tokens);
   const bool vec = (D / 2) % 4 == 0;
 #define LSE_ROPE_VEC(TIn, T)                                                                      \
-  rope_kv_write_vec_kernel<TIn, T><<<T_, 256, 0, stream>>>(                                       \
-      (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,         \
-      (T*)v_pages, block_tables, table_stride, page_tokens, ps)
+  launch(rope_kv_write_vec_kernel<TIn, T>, T_, 256, 0, stream,                                   \
+         (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,      \
+         (T*)v_pages, block_tables, table_stride, page_tokens, ps)
   const int T_ = T;
   if (vec && in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ROPE_VEC(float, float);
   else if (vec && in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ROPE_VEC(bf16, bf16);
@@ -355,11 +363,11 @@ extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, 
   const int per_block = threads * 4;
   dim3 grid(T, min((I + per_block - 1) / per_block, 65535));
   if (in_dtype == LSE_F32 && dtype == LSE_F32)
-    silu_mul_kernel<float, float><<<grid, threads, 0, stream>>>((const float*)gu, (float*)out, I);
+    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I);
   else if (in_dtype == LSE_BF16 && dtype == LSE_BF16)
-    silu_mul_kernel<bf16, bf16><<<grid, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
   else if (in_dtype == LSE_F32 && dtype == LSE_BF16)
-    silu_mul_kernel<float, bf16><<<grid, threads, 0, stream>>>((const float*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();

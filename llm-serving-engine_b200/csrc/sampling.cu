@@ -74,6 +74,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
               const int* __restrict__ draw, int* __restrict__ out) {
   __shared__ float fs[32];
   __shared__ ArgMax as[32];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
   const float temp = temperature[r];
@@ -197,8 +199,8 @@ extern "C" int lse_sample(const float* logits, int R, int V, const float* temper
                           cudaStream_t stream) {
   if (R <= 0) return LSE_OK;
   if (V <= 0) return LSE_BAD_ARGUMENT;
-  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, temperature, top_k, top_p, min_p, seed,
-                                                  draw, out_tokens);
+  launch(sample_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, top_k, top_p, min_p,
+         seed, draw, out_tokens);
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 

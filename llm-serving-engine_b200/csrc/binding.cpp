@@ -94,7 +94,7 @@ void add_rmsnorm(Tensor& x, const OptTensor& residual, const Tensor& weight, dou
 Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tensor& positions,
                      const Tensor& token_seq, const OptTensor& cos, const OptTensor& sin,
                      const OptTensor& k_pages, const OptTensor& v_pages, const Tensor& block_tables,
-                     int64_t page_tokens, bool q_bf16) {
+                     int64_t page_tokens, bool q_bf16, bool zero_in) {
   check_cuda(qkv, "qkv");
   check_i32(positions, "positions");
   check_i32(token_seq, "token_seq");
@@ -135,19 +135,19 @@ Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tenso
   done(lse_rope_kv_write(qkv.data_ptr(), in_code, q.data_ptr(), out_code, T, (int)nq, (int)nk, (int)D,
                          positions.data_ptr<int>(), token_seq.data_ptr<int>(), c, s, kp, vp,
                          block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens,
-                         stream()),
+                         zero_in ? 1 : 0, stream()),
        "rope_kv_write");
   return q;
 }
 
-void silu_mul(const Tensor& gu, Tensor& out) {
+void silu_mul(const Tensor& gu, Tensor& out, bool zero_in) {
   check_cuda(gu, "gu");
   check_cuda(out, "out");
   TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(1) == 2 * out.size(1) &&
                   gu.size(0) == out.size(0),
               "silu_mul: gu must be [T, 2I] and out [T, I]");
   done(lse_silu_mul(gu.data_ptr(), dtype_code(gu, "gu"), out.data_ptr(), dtype_code(out, "out"),
-                    (int)gu.size(0), (int)out.size(1), stream()),
+                    (int)gu.size(0), (int)out.size(1), zero_in ? 1 : 0, stream()),
        "silu_mul");
 }
 

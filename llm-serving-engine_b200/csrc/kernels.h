@@ -34,11 +34,14 @@ int lse_add_rmsnorm(float* x, const void* residual, int residual_dtype, const fl
 int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int dtype, int T, int nq, int nk,
                       int D, const int* positions, const int* token_seq, const float* cos,
                       const float* sin, void* k_pages, void* v_pages, const int* block_tables,
-                      int table_stride, int page_tokens, cudaStream_t stream);
+                      int table_stride, int page_tokens, int zero_in, cudaStream_t stream);
 
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]     gu [T, 2I] of in_dtype, out [T, I] of dtype
-// (in_dtype == dtype, or float32 in and bfloat16 out)
-int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I, cudaStream_t stream);
+// (in_dtype == dtype, or float32 in and bfloat16 out). zero_in = 1 (float32 in, bfloat16 out
+// only; also for lse_rope_kv_write): the input is an accumulation buffer of the few-rows matrix
+// product; every element that is read is set to zero, so the buffer is ready for the next product.
+int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I, int zero_in,
+                 cudaStream_t stream);
 
 // True float32 matrix product: out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]). Each output element is
 // accumulated over k in ascending order by one thread, so a row's result does not depend on T.

@@ -195,7 +195,7 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
                                          const float* __restrict__ sin_t, T* __restrict__ k_pages,
                                          T* __restrict__ v_pages,
                                          const int* __restrict__ block_tables, int table_stride,
-                                         int page_tokens, int page_shift) {
+                                         int page_tokens, int page_shift, int zero_in) {
   constexpr int V = 4;  // elements per item and half
   pdl_trigger();
   pdl_wait();
@@ -213,13 +213,19 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
   }
   const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
   const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
-  const int n_items = ((nq + nk) + (k_pages ? nk : 0)) * chunks;
+  // zero_in: the input is a float32 accumulation buffer that must read as zero afterwards
+  const int n_items = ((nq + nk) + ((k_pages || zero_in) ? nk : 0)) * chunks;
   for (int it = threadIdx.x; it < n_items; it += blockDim.x) {
     const int head = it / chunks, i = (it - head * chunks) * V;
     const TIn* h = row + (size_t)head * D;
     float a[4], b[4];
     load4<TIn>(h + i, a);
     load4<TIn>(h + i + half, b);
+    if (!std::is_same<TIn, T>::value && zero_in) {
+      const float z[4] = {0.f, 0.f, 0.f, 0.f};
+      store4<TIn>(const_cast<TIn*>(h) + i, z);
+      store4<TIn>(const_cast<TIn*>(h) + i + half, z);
+    }
     if (head < nq + nk && c) {
       float cv[4], sv[4];
       load4<float>(c + i, cv);
@@ -247,7 +253,7 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
 
 // ------------------------------------------------------------------------------------ silu * up
 template <typename TIn, typename T>
-__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I) {
+__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I, int zero_in) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -259,6 +265,11 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out,
       float gv[4], uv[4];
       load4<TIn>(g + i, gv);
       load4<TIn>(u + i, uv);
+      if (!std::is_same<TIn, T>::value && zero_in) {  // accumulation buffer: leave zeros behind
+        const float z[4] = {0.f, 0.f, 0.f, 0.f};
+        store4<TIn>(const_cast<TIn*>(g) + i, z);
+        store4<TIn>(const_cast<TIn*>(u) + i, z);
+      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) gv[j] = gv[j] / (1.f + expf(-gv[j])) * uv[j];
       store4<T>(o + i, gv);
@@ -324,8 +335,9 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
                                  int nk, int D, const int* positions, const int* token_seq,
                                  const float* cos, const float* sin, void* k_pages, void* v_pages,
                                  const int* block_tables, int table_stride, int page_tokens,
-                                 cudaStream_t stream) {
+                                 int zero_in, cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
+  if (zero_in && !(in_dtype == LSE_F32 && dtype == LSE_BF16 && (D / 2) % 4 == 0)) return LSE_BAD_ARGUMENT;
   if (D % 2 || page_tokens <= 0 || (cos == nullptr) != (sin == nullptr) ||
       (k_pages == nullptr) != (v_pages == nullptr))
     return LSE_BAD_ARGUMENT;
@@ -336,7 +348,7 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
 #define LSE_ROPE_VEC(TIn, T)                                                                      \
   launch(rope_kv_write_vec_kernel<TIn, T>, T_, 256, 0, stream,                                   \
          (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,      \
-         (T*)v_pages, block_tables, table_stride, page_tokens, ps)
+         (T*)v_pages, block_tables, table_stride, page_tokens, ps, zero_in)
   const int T_ = T;
   if (vec && in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ROPE_VEC(float, float);
   else if (vec && in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ROPE_VEC(bf16, bf16);
@@ -357,17 +369,18 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
 }
 
 extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I,
-                            cudaStream_t stream) {
+                            int zero_in, cudaStream_t stream) {
   if (T <= 0 || I <= 0) return LSE_OK;
+  if (zero_in && !(in_dtype == LSE_F32 && dtype == LSE_BF16 && I % 4 == 0)) return LSE_BAD_ARGUMENT;
   const int threads = 256;
   const int per_block = threads * 4;
   dim3 grid(T, min((I + per_block - 1) / per_block, 65535));
   if (in_dtype == LSE_F32 && dtype == LSE_F32)
-    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I);
+    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I, 0);
   else if (in_dtype == LSE_BF16 && dtype == LSE_BF16)
-    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I, 0);
   else if (in_dtype == LSE_F32 && dtype == LSE_BF16)
-    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I);
+    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I, zero_in);
   else
     return LSE_BAD_ARGUMENT;
   return LSE_CHECK_LAUNCH();

@@ -35,6 +35,10 @@ class CudaOps:
         self.use_skinny_gemm = True
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
         self.skinny_atomic_rows = 64  # above this the atomics' traffic is no longer small
+        # float32 accumulation buffers of the few-rows product, by shape. Invariant: a buffer that
+        # is not in _ws_live reads as zero (the kernel that consumes a product zeroes what it reads).
+        self._ws: dict[tuple[int, int], torch.Tensor] = {}
+        self._ws_live: dict[int, tuple[int, int]] = {}  # data_ptr -> shape of products not yet consumed
         self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
 
     # ------------------------------------------------------------------ capabilities
@@ -79,9 +83,38 @@ class CudaOps:
         self.launches += 1
         return out
 
+    def _accumulator(self, T: int, N: int) -> torch.Tensor:
+        """A zero float32 ``[T, N]`` buffer for atomic sums: the persistent one of this shape if its
+        last product has been consumed, else a fresh one."""
+        ws = self._ws.get((T, N))
+        if ws is None and not torch.cuda.is_current_stream_capturing():
+            ws = self._ws[(T, N)] = torch.zeros(T, N, dtype=torch.float32, device=self.device)
+        if ws is None or ws.data_ptr() in self._ws_live:
+            return torch.zeros(T, N, dtype=torch.float32, device=self.device)
+        self._ws_live[ws.data_ptr()] = (T, N)
+        return ws
+
+    def _consumes(self, t: torch.Tensor, out_dtype, kernel_can_zero: bool) -> bool:
+        """True if ``t`` is a live accumulation buffer that the consuming kernel will zero."""
+        if t.data_ptr() not in self._ws_live:
+            return False
+        if t.dtype == torch.float32 and out_dtype == torch.bfloat16 and kernel_can_zero:
+            del self._ws_live[t.data_ptr()]
+            return True
+        return False
+
+    def _release(self, t: torch.Tensor) -> None:
+        """``t`` was read by a kernel that did not zero it: restore the zero invariant."""
+        if self._ws_live.pop(t.data_ptr(), None) is not None:
+            t.zero_()
+
     def silu_mul(self, gu, out_dtype=None):
-        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=out_dtype or gu.dtype, device=gu.device)
-        self.ext.silu_mul(gu, out)
+        out_dtype = out_dtype or gu.dtype
+        out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=out_dtype, device=gu.device)
+        zero = self._consumes(gu, out_dtype, gu.shape[1] % 8 == 0)
+        self.ext.silu_mul(gu, out, zero)
+        if not zero:
+            self._release(gu)
         self.launches += 1
         return out
 
@@ -91,7 +124,9 @@ class CudaOps:
 
         out_dtype None asks for "an activation for the next kernel of this package": the compute
         dtype, or float32 sums where those come for free (the kernels that read activations take
-        both). With ``accumulate_into`` (a float32 tensor of the result's shape) the product may be
+        both; a float32 result may be an internal accumulation buffer that ``rope_kv_write`` or
+        ``silu_mul`` clears as it reads it, so it must not be read again after that).
+        With ``accumulate_into`` (a float32 tensor of the result's shape) the product may be
         added into that tensor instead; the return value is then None.
         """
         if a.dtype == torch.float32:
@@ -117,7 +152,8 @@ class CudaOps:
                 self.ext.gemm_bf16_skinny(a, w, bias, accumulate_into, True)
                 self.launches += 1
                 return None
-            out = torch.zeros(T, N, dtype=torch.float32, device=a.device)
+            out = (self._accumulator(T, N) if out_dtype is None
+                   else torch.zeros(T, N, dtype=torch.float32, device=a.device))
             self.ext.gemm_bf16_skinny(a, w, bias, out, True)
             self.launches += 1
             return out
@@ -134,9 +170,12 @@ class CudaOps:
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
                       cos, sin, k_pages, v_pages, block_tables, page_tokens, out_dtype):
         """Rotate q and k, write k and v into their pages; returns the rotated queries."""
+        zero = self._consumes(qkv, out_dtype, head_dim % 8 == 0)
         q = self.ext.rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, positions, token_seq,
                                    cos, sin, k_pages, v_pages, block_tables, page_tokens,
-                                   out_dtype == torch.bfloat16)
+                                   out_dtype == torch.bfloat16, zero)
+        if not zero:
+            self._release(qkv)
         self.launches += 1
         return q
 

@@ -12,10 +12,15 @@
 //
 // Three kernels:
 //   prefill_simt  portions of >= 2 rows, any dtype: 32 rows per block, 4 threads per row.
-//   prefill_mma   bfloat16 portions, D <= 128: 64 rows per block on mma.sync tensor cores.
+//   prefill_mma   bfloat16 portions, D <= 128: 128 rows per block (8 warps) on mma.sync tensor
+//                 cores; key/value tiles of 64 tokens are double-buffered with cp.async.
 //   decode_split  single rows: the context is cut into partitions, one block per (partition,
-//                 head group, sequence); partial (max, sum, weighted values) are merged by
-//                 decode_merge (src/llmserve/kernels/csrc/paged_attention.cpp:245-346).
+//                 head group, sequence); partial (max, sum, weighted values) go to scratch and the
+//                 block that finishes last for a (sequence, head group) merges them
+//                 (src/llmserve/kernels/csrc/paged_attention.cpp:245-346 merges in a second pass).
+//                 The scratch starts with LSE_ATTN_COUNTERS int counters (one per (sequence,
+//                 head group) is used), then the partial results; the counters must be zero
+//                 before a launch and are zero again after it.
 #include "attention_args.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -155,7 +160,7 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
 }
 
 // ============================================================================ prefill, tensor cores
-constexpr int MMA_QT = 64, MMA_KT = 64;
+constexpr int MMA_QT = 128, MMA_KT = 64, MMA_THREADS = 256;  // 8 warps x 16 query rows
 constexpr bool kHasMma = (D <= 128);
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
@@ -189,13 +194,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 #if LSE_HEAD_DIM <= 128
-__global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, int page_shift) {
+__global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) prefill_mma_kernel(const LseAttnArgs a, int page_shift) {
   constexpr int QT = MMA_QT, KT = MMA_KT, LD = D + 8, NCHUNK = D / 8, KS = D / 16, NB = KT / 8,
                 DB = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [QT][LD]
-  bf16* ks = qs + QT * LD;                       // [KT][LD]
-  bf16* vs = ks + KT * LD;                       // [KT][LD]
+  bf16* ks_all = qs + QT * LD;                   // [2][KT][LD]: the next tile loads while one is used
+  bf16* vs_all = ks_all + 2 * KT * LD;           // [2][KT][LD]
   const int seq = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
   const int head = blockIdx.y;
   const int kvh = head / (a.num_heads / a.num_kv_heads);
@@ -231,9 +236,11 @@ __global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, i
   const float sl2 = a.scale * 1.4426950408889634f;  // scores in the base-2 domain
   const int qpos_r[2] = {si.pos0 + q0 + warp * 16 + g, si.pos0 + q0 + warp * 16 + g + 8};
   const bool valid_r[2] = {warp * 16 + g < rows_here, warp * 16 + g + 8 < rows_here};
+  const int qmin_w = si.pos0 + q0 + warp * 16;  // position of this warp's first query row
 
-  for (int k0 = (k_first / KT) * KT; k0 < k_end; k0 += KT) {
-    __syncthreads();  // everyone is done with the previous tile
+  auto load_tile = [&](int buf, int k0) {
+    bf16* ks = ks_all + buf * KT * LD;
+    bf16* vs = vs_all + buf * KT * LD;
     for (int idx = threadIdx.x; idx < KT * NCHUNK; idx += blockDim.x) {
       const int jj = idx / NCHUNK, c = idx - jj * NCHUNK;
       const int j = k0 + jj;
@@ -248,8 +255,20 @@ __global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, i
       cp_async16(vs + jj * LD + c * 8, vp + base, ok);
     }
     asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::);
+  };
+  const int k_start = (k_first / KT) * KT;
+  if (k_start < k_end) load_tile(0, k_start);
+  int buf = 0;
+  for (int k0 = k_start; k0 < k_end; k0 += KT, buf ^= 1) {
+    if (k0 + KT < k_end) {
+      load_tile(buf ^ 1, k0 + KT);  // that buffer was released by the barrier that ended the last pass
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
     __syncthreads();
+    const bf16* ks = ks_all + buf * KT * LD;
+    const bf16* vs = vs_all + buf * KT * LD;
 
     // S = Q K^T for 16 rows x 64 keys
     float s[NB][4];
@@ -266,28 +285,40 @@ __global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, i
         mma_bf16(s[nb + 1], qf[kk], b[2], b[3]);
       }
     }
-    // mask, running maximum
+    // running maximum; only tiles on the diagonal, at a window's edge or at the context's start
+    // need the per-element mask (rows past the portion compute garbage that is never stored)
+    const bool full_tile = k0 >= k_first && k0 + KT - 1 <= qmin_w &&
+                           (a.window <= 0 || qmin_w + 15 - k0 < a.window);
     float tmax[2] = {-INFINITY, -INFINITY};
+    if (full_tile) {
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
+      for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int rr = e >> 1;
-        const int j = k0 + nb * 8 + t4 * 2 + (e & 1);
-        const bool ok = valid_r[rr] && j <= qpos_r[rr] && j >= k_first &&
-                        (a.window <= 0 || j > qpos_r[rr] - a.window);
-        s[nb][e] = ok ? s[nb][e] * sl2 : -INFINITY;
-        tmax[rr] = fmaxf(tmax[rr], s[nb][e]);
+        for (int e = 0; e < 4; ++e) tmax[e >> 1] = fmaxf(tmax[e >> 1], s[nb][e]);
+    } else {
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int rr = e >> 1;
+          const int j = k0 + nb * 8 + t4 * 2 + (e & 1);
+          const bool ok = valid_r[rr] && j <= qpos_r[rr] && j >= k_first &&
+                          (a.window <= 0 || j > qpos_r[rr] - a.window);
+          s[nb][e] = ok ? s[nb][e] : -INFINITY;
+          tmax[rr] = fmaxf(tmax[rr], s[nb][e]);
+        }
       }
     }
+    // scores stay unscaled; the scale (times log2 e) is folded into the exponent's multiply-add
     float corr[2], m_use[2];
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
       tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
       tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
       const float m_new = fmaxf(m_r[rr], tmax[rr]);
-      m_use[rr] = (m_new == -INFINITY) ? 0.f : m_new;  // keeps exp2f(-inf - m_use) = 0, not NaN
-      corr[rr] = exp2f(m_r[rr] - m_use[rr]);
+      const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;  // keeps exp2f(-inf - m) = 0, not NaN
+      corr[rr] = exp2f((m_r[rr] - m_fin) * sl2);
+      m_use[rr] = m_fin * sl2;
       m_r[rr] = m_new;
       l_r[rr] *= corr[rr];
     }
@@ -307,7 +338,7 @@ __global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, i
       for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          p[h][e] = exp2f(s[2 * kb + h][e] - m_use[e >> 1]);
+          p[h][e] = exp2f(fmaf(s[2 * kb + h][e], sl2, -m_use[e >> 1]));
           l_r[e >> 1] += p[h][e];
         }
       pa[0] = pack_bf16(p[0][0], p[0][1]);
@@ -323,6 +354,7 @@ __global__ void __launch_bounds__(128) prefill_mma_kernel(const LseAttnArgs a, i
         mma_bf16(o[db + 1], pa, b[2], b[3]);
       }
     }
+    __syncthreads();  // all warps are done with this tile's buffers
   }
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
@@ -516,7 +548,8 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
       T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
       o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
     } else {
-      float* part = a.scratch + (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
+      float* part = a.scratch + LSE_ATTN_COUNTERS +
+                    (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
       part[d] = A;
       if (d == 0) {
         part[D] = M;
@@ -524,25 +557,34 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
       }
     }
   }
-}
-
-template <typename T>
-__global__ void decode_merge_kernel(const LseAttnArgs a) {
-  pdl_trigger();
-  pdl_wait();
-  const int b = blockIdx.x, h = blockIdx.y;
-  const int seq = a.decode_seqs[b];
-  const int tok = a.cu_q[seq];
-  const float* part = a.scratch + ((size_t)b * a.num_heads + h) * a.num_splits * (D + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < a.num_splits; ++s) M = fmaxf(M, part[s * (D + 2) + D]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  if (a.num_splits == 1) return;
+  // The block that finishes last for this (sequence, head group) merges the partitions. Counters
+  // live behind the partial results, start at zero and are reset by the merging block.
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = reinterpret_cast<int*>(a.scratch) + (size_t)b * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(counter, 1);
+    is_last = (done == a.num_splits - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += blockDim.x) {
+    const int gq = idx / D, d = idx - gq * D;
+    const int h = h0 + gq;
+    const float* part =
+        a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h) * a.num_splits * (D + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < a.num_splits; ++s) M = fmaxf(M, __ldcg(part + s * (D + 2) + D));
     float L = 0.f, A = 0.f;
     for (int s = 0; s < a.num_splits; ++s) {
-      const float ms = part[s * (D + 2) + D];
+      const float ms = __ldcg(part + s * (D + 2) + D);
       const float wt = (ms == -INFINITY) ? 0.f : Exp<T>::f(ms - M);
-      L += part[s * (D + 2) + D + 1] * wt;
-      A += part[s * (D + 2) + d] * wt;
+      L += __ldcg(part + s * (D + 2) + D + 1) * wt;
+      A += __ldcg(part + s * (D + 2) + d) * wt;
     }
     T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
     o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
@@ -570,16 +612,11 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
   dim3 grid(a->num_splits, a->num_kv_heads * ((G + gt - 1) / gt), a->num_decode);
   if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
+  if (a->num_splits > 1 && (size_t)grid.y * grid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
   if (gt == 1) launch(decode_split_kernel<T, 1>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   else if (gt == 2) launch(decode_split_kernel<T, 2>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   else launch(decode_split_kernel<T, 4>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
-  if (cudaGetLastError() != cudaSuccess) return LSE_LAUNCH_FAILED;
-  if (a->num_splits > 1) {
-    dim3 mgrid(a->num_decode, a->num_heads);
-    launch(decode_merge_kernel<T>, mgrid, D < 32 ? 32 : (D > 128 ? 128 : D), 0, stream, *a);
-    if (cudaGetLastError() != cudaSuccess) return LSE_LAUNCH_FAILED;
-  }
-  return LSE_OK;
+  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 }  // namespace lse
@@ -593,7 +630,9 @@ extern "C" int lse_attn_q_tile(int dtype) {
 }
 
 extern "C" size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, int num_splits) {
-  return num_splits > 1 ? (size_t)num_decode * num_heads * num_splits * (D + 2) : 0;
+  // a fixed region of completion counters, then the partial results
+  return num_splits > 1 ? (size_t)LSE_ATTN_COUNTERS + (size_t)num_decode * num_heads * num_splits * (D + 2)
+                        : 0;
 }
 
 extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
@@ -609,7 +648,7 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
     prefill_simt_kernel<bf16><<<grid, 128, 0, stream>>>(*a, ps);
   } else {
 #if LSE_HEAD_DIM <= 128
-    constexpr int smem = (MMA_QT + 2 * MMA_KT) * (D + 8) * (int)sizeof(bf16);
+    constexpr int smem = (MMA_QT + 4 * MMA_KT) * (D + 8) * (int)sizeof(bf16);
     static bool configured = false;
     if (!configured) {
       if (cudaFuncSetAttribute(prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -617,7 +656,7 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
         return LSE_LAUNCH_FAILED;
       configured = true;
     }
-    prefill_mma_kernel<<<grid, 128, smem, stream>>>(*a, ps);
+    prefill_mma_kernel<<<grid, MMA_THREADS, smem, stream>>>(*a, ps);
 #endif
   }
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;

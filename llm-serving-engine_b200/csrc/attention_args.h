@@ -32,8 +32,12 @@ struct LseAttnArgs {
   const int* decode_seqs;  // [num_decode] sequence indices with one row each
   int num_decode;
   int num_splits;          // context partitions per (sequence, head)
-  float* scratch;          // float32 [num_decode * num_heads * num_splits * (D + 2)] if num_splits > 1
+  float* scratch;          // if num_splits > 1: lse_attn_decode_scratch_floats(...) floats; its
+                           // first LSE_ATTN_COUNTERS words are counters that must be zero before
+                           // a launch (every launch leaves them zero)
 };
+
+#define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)
 
 int lse_attn_head_dim(void);
 // rows per tile that lse_attn_prefill expects in `tiles` for this dtype
@@ -54,13 +58,15 @@ int lse_attn_decode(const LseAttnArgs* a, cudaStream_t stream);
 // inputs and the output; `a->scratch` is ignored. The function calls no cudaMalloc, cudaFree or
 // other allocating routine.
 //
-//  * Size limit: num_decode * num_heads * num_splits * (D + 2) must not exceed
+//  * Size limit: lse_attn_decode_scratch_floats(num_decode, num_heads, num_splits) must not exceed
 //    LSE_ATTN_NOALLOC_MAX_FLOATS when num_splits > 1; otherwise nothing is launched and
 //    LSE_TOO_LARGE is returned (lse_attn_decode_noalloc_max_floats() reports the limit).
 //  * First call on a device: it looks up the buffer's device address (cudaGetSymbolAddress, with
 //    that device current) and remembers it. Make that first call outside any stream capture.
-//  * The buffer is shared by every call and keeps the last call's contents. Nothing in it has to
-//    start at zero: each launch writes every partial result it later reads. Two calls whose
+//  * The buffer is shared by every call and keeps the last call's contents. The partial results
+//    need no clearing (each launch writes every one it later reads); the completion counters
+//    must start at zero, which holds because the buffer is zero when the library is loaded and
+//    every launch resets the counters it used. Two calls whose
 //    kernels overlap on the GPU (different streams) would race on it; run them one after the other.
 #define LSE_ATTN_NOALLOC_MAX_FLOATS (1 << 20)
 #define LSE_TOO_LARGE 3

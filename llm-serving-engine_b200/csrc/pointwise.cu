@@ -215,7 +215,7 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
   const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
   // zero_in: the input is a float32 accumulation buffer that must read as zero afterwards
   const int n_items = ((nq + nk) + ((k_pages || zero_in) ? nk : 0)) * chunks;
-  for (int it = threadIdx.x; it < n_items; it += blockDim.x) {
+  for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < n_items; it += gridDim.y * blockDim.x) {
     const int head = it / chunks, i = (it - head * chunks) * V;
     const TIn* h = row + (size_t)head * D;
     float a[4], b[4];
@@ -346,10 +346,12 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
   const int ps = shift_of(page_tokens);
   const bool vec = (D / 2) % 4 == 0;
 #define LSE_ROPE_VEC(TIn, T)                                                                      \
-  launch(rope_kv_write_vec_kernel<TIn, T>, T_, 256, 0, stream,                                   \
+  launch(rope_kv_write_vec_kernel<TIn, T>, vgrid, 128, 0, stream,                                 \
          (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,      \
          (T*)v_pages, block_tables, table_stride, page_tokens, ps, zero_in)
-  const int T_ = T;
+  // one thread per item (head, chunk of 4 + 4 elements): every load of a token is in flight at once
+  const int items = (nq + 2 * nk) * (D / 8);
+  const dim3 vgrid(T, (items + 127) / 128 > 64 ? 64 : (items + 127) / 128);
   if (vec && in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ROPE_VEC(float, float);
   else if (vec && in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ROPE_VEC(bf16, bf16);
   else if (vec && in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_ROPE_VEC(float, bf16);

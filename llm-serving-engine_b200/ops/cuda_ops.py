@@ -37,6 +37,7 @@ class CudaOps:
         self.skinny_atomic_rows = 64  # above this the atomics' traffic is no longer small
         # float32 accumulation buffers of the few-rows product, by shape. Invariant: a buffer that
         # is not in _ws_live reads as zero (the kernel that consumes a product zeroes what it reads).
+        self._addmm_in_place: bool | None = None  # whether torch.addmm can add into a float32 tensor
         self._ws: dict[tuple[int, int], torch.Tensor] = {}
         self._ws_live: dict[int, tuple[int, int]] = {}  # data_ptr -> shape of products not yet consumed
         self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
@@ -60,7 +61,8 @@ class CudaOps:
         if self._scratch is None or self._scratch.numel() < need:
             if torch.cuda.is_current_stream_capturing():
                 raise RuntimeError("attention scratch must be reserved before graph capture")
-            self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
+            # zeros: the buffer starts with completion counters that every launch leaves at zero
+            self._scratch = torch.zeros(need, dtype=torch.float32, device=self.device)
 
     def check_kernel_errors(self) -> None:
         """Raise if a kernel recorded that one of its bounded waits ran out."""
@@ -157,6 +159,16 @@ class CudaOps:
             self.ext.gemm_bf16_skinny(a, w, bias, out, True)
             self.launches += 1
             return out
+        if accumulate_into is not None and bias is None and self._addmm_in_place is not False:
+            # many rows: the library adds the product into the residual stream (beta = 1)
+            try:
+                torch.addmm(accumulate_into, a, w.t(), out_dtype=torch.float32, out=accumulate_into)
+                self._addmm_in_place = True
+                return None
+            except (RuntimeError, TypeError):
+                if self._addmm_in_place:
+                    raise
+                self._addmm_in_place = False  # this build of the library cannot; use the plain form
         if out_dtype == torch.float32:
             out = torch.mm(a, w.t(), out_dtype=torch.float32)
             if bias is not None:
@@ -225,7 +237,7 @@ class CudaOps:
             plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,
             self.force_simt_attention,
         )
-        self.launches += (1 if n_tiles else 0) + (0 if not n_dec else (2 if splits > 1 else 1))
+        self.launches += (1 if n_tiles else 0) + (1 if n_dec else 0)
         return out
 
     # ------------------------------------------------------------------ sampling

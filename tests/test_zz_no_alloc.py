@@ -97,7 +97,7 @@ def test_no_alloc_entry_point_matches_the_allocating_one_twice_in_a_row(lib, dty
         need = lib.lse_attn_decode_scratch_floats(t["B"], NQ, splits)
         assert 0 < need <= lib.lse_attn_decode_noalloc_max_floats()
         ref = torch.zeros(t["B"], NQ * D, dtype=dtype, device="cuda")
-        scratch = torch.empty(need, dtype=torch.float32, device="cuda")
+        scratch = torch.zeros(need, dtype=torch.float32, device="cuda")  # its counters start at zero
         assert lib.lse_attn_decode(ctypes.byref(args_for(t, ref, scratch)), stream) == 0
         got = torch.full_like(ref, 7.0)
         assert lib.lse_attn_decode_noalloc(ctypes.byref(args_for(t, got, None)), stream) == 0

@@ -12,6 +12,8 @@
 //
 // Three kernels:
 //   prefill_simt  portions of >= 2 rows, any dtype: 32 rows per block, 4 threads per row.
+//   prefill_tc    (attention_tc.cuh) bfloat16 portions, D = 64, no window: tcgen05 tensor cores with
+//                 TMA-fed operands and accumulators in tensor memory.
 //   prefill_mma   bfloat16 portions, D <= 128: 128 rows per block (8 warps) on mma.sync tensor
 //                 cores; key/value tiles of 64 tokens are double-buffered with cp.async.
 //   decode_split  single rows: the context is cut into partitions, one block per (partition,
@@ -24,6 +26,9 @@
 #include "attention_args.h"
 #include "common.cuh"
 #include "kernels.h"
+#if LSE_HEAD_DIM == 64
+#include "attention_tc.cuh"
+#endif
 
 #ifndef LSE_HEAD_DIM
 #error "compile with -DLSE_HEAD_DIM=<head size>"
@@ -643,7 +648,13 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
   dim3 grid(a->num_tiles, a->num_heads);
   if (a->dtype == LSE_F32) {
     prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
-  } else if (!kHasMma || a->force_simt) {
+#if LSE_HEAD_DIM == 64
+  } else if (a->force_simt == 0 && a->num_rows > 0 && a->num_pages > 0 && atc::supported(a)) {
+    // 128-row tiles, like the mma.sync kernel
+    return atc::launch_prefill(a, a->num_rows, a->num_pages * a->num_kv_heads * a->page_tokens,
+                               a->error_flag, stream);
+#endif
+  } else if (!kHasMma || a->force_simt == 1) {
     // the caller built tiles of SIMT_QT rows in this case
     prefill_simt_kernel<bf16><<<grid, 128, 0, stream>>>(*a, ps);
   } else {

@@ -27,7 +27,8 @@ struct LseAttnArgs {
   // portions of two or more tokens
   const int* tiles;        // [num_tiles, 2]: sequence, first row of the tile within its portion
   int num_tiles;
-  int force_simt;          // run the CUDA-core kernel even where a tensor-core one exists
+  int force_simt;          // 0: fastest kernel that serves the arguments; 1: the CUDA-core kernel;
+                           // 2: the mma.sync tensor-core kernel (no tcgen05)
   // single tokens
   const int* decode_seqs;  // [num_decode] sequence indices with one row each
   int num_decode;
@@ -35,6 +36,10 @@ struct LseAttnArgs {
   float* scratch;          // if num_splits > 1: lse_attn_decode_scratch_floats(...) floats; its
                            // first LSE_ATTN_COUNTERS words are counters that must be zero before
                            // a launch (every launch leaves them zero)
+  // sizes of the tensors behind q/out and the pages (needed to describe them to TMA)
+  long long num_rows;      // rows of q and out
+  long long num_pages;     // pages in k_pages / v_pages
+  int* error_flag;         // device-visible int that receives a code if a bounded wait ran out, or null
 };
 
 #define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)

@@ -246,9 +246,9 @@ const AttnLib& attn_lib(int64_t D) {
   return it->second;
 }
 
-int64_t attention_q_tile(int64_t D, bool bf16, bool force_simt) {
+int64_t attention_q_tile(int64_t D, bool bf16, int64_t force_kernel) {
   const AttnLib& lib = attn_lib(D);
-  return force_simt ? lib.q_tile(LSE_F32) : lib.q_tile(bf16 ? LSE_BF16 : LSE_F32);
+  return force_kernel == 1 ? lib.q_tile(LSE_F32) : lib.q_tile(bf16 ? LSE_BF16 : LSE_F32);
 }
 
 int64_t attention_scratch_floats(int64_t D, int64_t num_decode, int64_t num_heads, int64_t splits) {
@@ -262,7 +262,7 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
                      int64_t window, const Tensor& block_tables, const Tensor& ctx_lens,
                      const Tensor& cu_q, const OptTensor& tiles, int64_t num_tiles,
                      const OptTensor& decode_seqs, int64_t num_decode, int64_t num_splits,
-                     const OptTensor& scratch, bool force_simt) {
+                     const OptTensor& scratch, int64_t force_kernel) {
   const AttnLib& lib = attn_lib(D);
   TORCH_CHECK(q.is_cuda() && q.dim() == 2 && q.stride(1) == 1 && q.size(1) >= num_heads * D,
               "paged_attention: q must be [T, >= heads*head_dim] with unit column stride");
@@ -303,7 +303,10 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
   a.table_stride = (int)block_tables.size(1);
   a.ctx_lens = ctx_lens.data_ptr<int>();
   a.cu_q = cu_q.data_ptr<int>();
-  a.force_simt = force_simt ? 1 : 0;
+  a.force_simt = (int)force_kernel;
+  a.num_rows = q.size(0);
+  a.num_pages = k_pages.size(0);
+  a.error_flag = error_flag();
   if (num_tiles > 0) {
     TORCH_CHECK(tiles.has_value(), "paged_attention: num_tiles > 0 without tiles");
     check_i32(*tiles, "tiles");

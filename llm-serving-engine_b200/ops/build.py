@@ -28,7 +28,7 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--expt-relaxed-constexpr"]
 CORE_CU = ["pointwise.cu", "gemm_f32.cu", "gemm_bf16_tc.cu", "sampling.cu"]
-CORE_HEADERS = ["common.cuh", "kernels.h", "attention_args.h", "status.h"]
+CORE_HEADERS = ["common.cuh", "kernels.h", "attention_args.h", "status.h", "tma_util.cuh", "attention_tc.cuh"]
 
 _core = None
 _attn_paths: dict[int, str] = {}

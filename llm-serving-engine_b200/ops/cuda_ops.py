@@ -31,7 +31,7 @@ class CudaOps:
         self._attn_loaded: set[int] = set()
         self._scratch: torch.Tensor | None = None
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.force_simt_attention = False
+        self.attention_kernel = 0  # 0: fastest available; 1: CUDA cores; 2: mma.sync (tests compare them)
         self.use_skinny_gemm = True
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
         self.skinny_atomic_rows = 64  # above this the atomics' traffic is no longer small
@@ -193,7 +193,7 @@ class CudaOps:
 
     def attention_q_tile(self, dtype, head_dim):
         return int(self.ext.attention_q_tile(head_dim, dtype == torch.bfloat16,
-                                             self.force_simt_attention))
+                                             self.attention_kernel))
 
     def attention_plan(self, host_step, dtype, head_dim):
         """Work lists for this step: tiles of the portions, and the single-token sequences."""
@@ -235,7 +235,7 @@ class CudaOps:
             int(window), block_tables, step.ctx_lens, step.cu_q,
             plan["tiles"] if n_tiles else None, n_tiles,
             plan["decode_seqs"] if n_dec else None, n_dec, splits, scratch,
-            self.force_simt_attention,
+            self.attention_kernel,
         )
         self.launches += (1 if n_tiles else 0) + (1 if n_dec else 0)
         return out

@@ -266,17 +266,43 @@ def test_one_far_key_stands_out(ops, dtype, far):
         close(got, ref, dtype, atol32=1e-5, rel16=0.02)
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16"])
-def test_tensor_core_and_cuda_core_prefill_agree(ops, dtype):
-    case = paged_case(2, [150, 64], [150, 200], 4, 2, 64, 16, torch.bfloat16, seed=3)
-    a, ref, _ = run_attention(ops, case, 4, 2, 64, 16, 0, 256)
-    ops.force_simt_attention = True
+@pytest.mark.parametrize("page", [8, 16, 64, 128])
+@pytest.mark.parametrize("nq,nk", [(4, 2), (3, 3)])
+def test_the_three_prefill_kernels_agree(ops, page, nq, nk):
+    """tcgen05 (head size 64), mma.sync and CUDA-core kernels on the same ragged batch."""
+    q_lens, ctx_lens = [150, 64, 2, 300, 129], [150, 200, 70, 300, 1000]
+    case = paged_case(5, q_lens, ctx_lens, nq, nk, 64, page, torch.bfloat16, seed=3)
+    outs = []
     try:
-        b, _, _ = run_attention(ops, case, 4, 2, 64, 16, 0, 256)
+        for kernel in (0, 1, 2):
+            ops.attention_kernel = kernel
+            got, ref, _ = run_attention(ops, case, nq, nk, 64, page, 0, 1024)
+            close(got, ref, "bfloat16", rel16=0.02)
+            outs.append(got.float().cpu())
     finally:
-        ops.force_simt_attention = False
-    close(a, ref, dtype, rel16=0.02)
-    close(b, ref, dtype, rel16=0.02)
+        ops.attention_kernel = 0
+    ops.check_kernel_errors()
+    assert (outs[0] - outs[1]).abs().max() <= 0.02 * outs[1].abs().max()
+
+
+@pytest.mark.parametrize("far", [0, 63, 64, 700, 1900])
+def test_tensor_core_prefill_finds_one_far_key(ops, far):
+    """A long portion whose last query looks at one key among two thousand (tcgen05 path)."""
+    nq = nk = 2
+    D, page, ctx, q_len = 64, 16, 2048, 130
+    case = paged_case(1, [q_len], [ctx], nq, nk, D, page, torch.bfloat16, seed=far + 7)
+    qkv, kp, vp, tables, positions, token_seq, step = case
+    qkv[-1, : nq * D] = 0
+    qkv[-1, 5] = 8.0
+    qkv[-1, D + 5] = 8.0
+    pg, off = int(tables[0, far // page]), far % page
+    kp[pg, :, off] = 0
+    kp[pg, :, off, 5] = 20.0
+    got, ref, _ = run_attention(ops, case, nq, nk, D, page, 0, ctx, rope=False)
+    want = vp[pg, :, off].float().reshape(-1)
+    assert (got[-1].float().cpu() - want).abs().max() < 0.02
+    close(got, ref, "bfloat16", rel16=0.02)
+    ops.check_kernel_errors()
 
 
 def test_unsupported_head_size_is_refused(ops):

@@ -32,6 +32,7 @@ class AttnArgs(ctypes.Structure):
         ("tiles", ctypes.c_void_p), ("num_tiles", ctypes.c_int), ("force_simt", ctypes.c_int),
         ("decode_seqs", ctypes.c_void_p), ("num_decode", ctypes.c_int), ("num_splits", ctypes.c_int),
         ("scratch", ctypes.c_void_p),
+        ("num_rows", ctypes.c_longlong), ("num_pages", ctypes.c_longlong), ("error_flag", ctypes.c_void_p),
     ]
 
 
@@ -85,6 +86,7 @@ def args_for(t, out, scratch):
     a.tiles, a.num_tiles, a.force_simt = None, 0, 0
     a.decode_seqs, a.num_decode, a.num_splits = t["seqs"].data_ptr(), t["B"], t["splits"]
     a.scratch = scratch.data_ptr() if scratch is not None else None
+    a.num_rows, a.num_pages, a.error_flag = t["B"], t["k"].shape[0], None
     return a
 
 

@@ -78,8 +78,9 @@ __global__ void __launch_bounds__(128) prefill_simt_kernel(const LseAttnArgs a, 
   constexpr int QT = SIMT_QT, KT = SIMT_KT, DPT = D / 4, VEC = Num<T>::kVec, NCHUNK = D / VEC;
   __shared__ float ks[KT][D];
   __shared__ float vs[KT][D];
-  const int seq = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
-  const int head = blockIdx.y;
+  // heads vary fastest over the grid, tiles (longest first) slowest
+  const int seq = a.tiles[2 * blockIdx.y], q0 = a.tiles[2 * blockIdx.y + 1];
+  const int head = blockIdx.x;
   const int kvh = head / (a.num_heads / a.num_kv_heads);
   const SeqInfo si = seq_info(a, seq);
   const int r = threadIdx.x >> 2, sub = threadIdx.x & 3;
@@ -206,8 +207,9 @@ __global__ void __launch_bounds__(MMA_THREADS, (LSE_HEAD_DIM <= 64 ? 2 : 1)) pre
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);  // [QT][LD]
   bf16* ks_all = qs + QT * LD;                   // [2][KT][LD]: the next tile loads while one is used
   bf16* vs_all = ks_all + 2 * KT * LD;           // [2][KT][LD]
-  const int seq = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
-  const int head = blockIdx.y;
+  // heads vary fastest over the grid, tiles (longest first) slowest
+  const int seq = a.tiles[2 * blockIdx.y], q0 = a.tiles[2 * blockIdx.y + 1];
+  const int head = blockIdx.x;
   const int kvh = head / (a.num_heads / a.num_kv_heads);
   const SeqInfo si = seq_info(a, seq);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
@@ -643,9 +645,9 @@ extern "C" size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, 
 extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
   if (!args_ok(a) || (a->num_tiles > 0 && !a->tiles)) return LSE_BAD_ARGUMENT;
   if (a->num_tiles <= 0) return LSE_OK;
-  if (a->num_heads > 65535) return LSE_BAD_ARGUMENT;
+  if (a->num_tiles > 65535) return LSE_BAD_ARGUMENT;
   const int ps = shift_of(a->page_tokens);
-  dim3 grid(a->num_tiles, a->num_heads);
+  dim3 grid(a->num_heads, a->num_tiles);
   if (a->dtype == LSE_F32) {
     prefill_simt_kernel<float><<<grid, 128, 0, stream>>>(*a, ps);
 #if LSE_HEAD_DIM == 64

@@ -29,7 +29,11 @@ constexpr int KT = 64;           // keys per tile
 constexpr int STAGES = 3;        // key/value tiles in flight
 constexpr int THREADS = 192;
 constexpr uint32_t Q_BYTES = QT * HD * 2, KV_BYTES = KT * HD * 2;
-constexpr uint32_t COL_S = 0, COL_P = 64, COL_O = 96, TMEM_COLS = 256;  // tensor-memory columns
+// Tensor-memory columns. S is double-buffered so that Q K^T of the next tile runs while the
+// softmax threads work on this one. P (32 packed columns) is written over the first half of the S
+// buffer it came from once the row is in registers; MMAs of one thread run in issue order, so a
+// later Q K^T into that buffer cannot overtake the P V that still reads P.
+constexpr uint32_t COL_S = 0, S_COLS = 64, COL_O = 128, TMEM_COLS = 256;
 
 __device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
   asm volatile(
@@ -69,6 +73,11 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32
         "r"(v[31])
       : "memory");
 }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -81,7 +90,7 @@ struct Params {
   int* error_flag;
 };
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -94,8 +103,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   uint64_t* q_full = bars;                 // [1]
   uint64_t* kv_full = bars + 1;            // [STAGES]
   uint64_t* kv_empty = kv_full + STAGES;   // [STAGES]
-  uint64_t* s_full = kv_empty + STAGES;    // S of this tile is in tensor memory
-  uint64_t* p_full = s_full + 1;           // P is written (and O rescaled): 4 arrivals
+  uint64_t* s_full = kv_empty + STAGES;    // [2] S of a tile is in tensor memory (buffer tile & 1)
+  uint64_t* p_full = s_full + 2;           // P is written (and O rescaled): 4 arrivals
   uint64_t* pv_done = p_full + 1;          // O += P V of this tile has finished
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 1);
   __shared__ volatile int failed;
@@ -103,8 +112,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
 
   const LseAttnArgs& a = p.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = a.tiles[2 * blockIdx.x], q0 = a.tiles[2 * blockIdx.x + 1];
-  const int head = blockIdx.y;
+  // heads vary fastest over the grid, tiles (longest first) slowest: every head's long tiles start early
+  const int seq = a.tiles[2 * blockIdx.y], q0 = a.tiles[2 * blockIdx.y + 1];
+  const int head = blockIdx.x;
   const int kvh = head / (a.num_heads / a.num_kv_heads);
   const int q_start = a.cu_q[seq];
   const int q_len = a.cu_q[seq + 1] - q_start;
@@ -126,7 +136,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    mbar_init(s_full, 1);
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
     mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -179,24 +190,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       constexpr uint32_t idesc_pv = instr_desc_bf16(QT, HD, 1);   // V tile N-major (rows are keys)
       bool ok = mbar_wait(q_full, 0);
       const uint64_t dq = smem_desc_sw128(smem_u32(q_tile));
-      for (int it = 0; it < n_tiles && ok && !failed; ++it) {
-        const int s = it % STAGES;
-        ok = mbar_wait(&kv_full[s], (it / STAGES) & 1);
-        if (!ok) break;
+      auto issue_qk = [&](int t) -> bool {  // S[t & 1] = Q K_t^T once tile t has landed
+        const int s = t % STAGES;
+        if (!mbar_wait(&kv_full[s], (t / STAGES) & 1)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t dk = smem_desc_sw128(smem_u32(k_tiles + s * KV_BYTES));
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)  // 16 head dims = 32 bytes along the swizzled row
-          umma_ss(tmem + COL_S, dq + 2 * kk, dk + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
-        umma_commit(s_full);
+          umma_ss(tmem + COL_S + (t & 1) * S_COLS, dq + 2 * kk, dk + 2 * kk, idesc_qk, kk > 0 ? 1u : 0u);
+        umma_commit(&s_full[t & 1]);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_qk(0);
+      for (int it = 0; it < n_tiles && ok && !failed; ++it) {
+        const int s = it % STAGES;
+        if (it + 1 < n_tiles) {  // the next tile's scores are computed while this tile's softmax runs
+          ok = issue_qk(it + 1);
+          if (!ok) break;
+        }
         ok = mbar_wait(p_full, it & 1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t dv = smem_desc_sw128(smem_u32(v_tiles + s * KV_BYTES));
 #pragma unroll
         for (int kk = 0; kk < KT / 16; ++kk)  // 16 keys = 16 rows of 128 bytes = 8 packed columns of P
-          umma_ts(tmem + COL_O, tmem + COL_P + 8 * kk, dv + (2048 >> 4) * kk, idesc_pv,
-                  (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + COL_O, tmem + COL_S + (it & 1) * S_COLS + 8 * kk, dv + (2048 >> 4) * kk,
+                  idesc_pv, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&kv_empty[s]);
         umma_commit(pv_done);
       }
@@ -213,15 +232,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int it = 0; it < n_tiles && !failed; ++it) {
-      ok = mbar_wait(s_full, it & 1);
+      ok = mbar_wait(&s_full[it & 1], (it >> 1) & 1);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t s_buf = lane_base + COL_S + (it & 1) * S_COLS;
       uint32_t sv[2][32];
-      tmem_ld32(lane_base + COL_S, sv[0]);
-      tmem_ld32(lane_base + COL_S + 32, sv[1]);
+      tmem_ld32(s_buf, sv[0]);
+      tmem_ld32(s_buf + 32, sv[1]);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const int k0 = it * KT;
-      float mx = m_run;
+      // four independent chains for the maximum and for the sum: a single chain of 64 dependent
+      // operations would leave the warp waiting on its own results
+      float mx4[4] = {m_run, -INFINITY, -INFINITY, -INFINITY};
       if (k0 + KT - 1 > pos0 + q0) {  // a tile that reaches the diagonal: mask per element
 #pragma unroll
         for (int h = 0; h < 2; ++h)
@@ -229,28 +251,30 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           for (int j = 0; j < 32; ++j) {
             const float v = (k0 + h * 32 + j <= qpos) ? __uint_as_float(sv[h][j]) : -INFINITY;
             sv[h][j] = __float_as_uint(v);
-            mx = fmaxf(mx, v);
+            mx4[j & 3] = fmaxf(mx4[j & 3], v);
           }
       } else {
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sv[h][j]));
+          for (int j = 0; j < 32; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sv[h][j]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_fin = (mx == -INFINITY) ? 0.f : mx;
-      const float corr = exp2f((m_run - m_fin) * sl2);  // m_run = -inf gives 0
+      const float corr = ex2((m_run - m_fin) * sl2);  // m_run = -inf gives 0
       const float ms = m_fin * sl2;
       m_run = mx;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const int h = j >> 4, c = (j & 15) * 2;
-        const float p0 = exp2f(fmaf(__uint_as_float(sv[h][c]), sl2, -ms));
-        const float p1 = exp2f(fmaf(__uint_as_float(sv[h][c + 1]), sl2, -ms));
-        sum += p0 + p1;
+        const float p0 = ex2(fmaf(__uint_as_float(sv[h][c]), sl2, -ms));
+        const float p1 = ex2(fmaf(__uint_as_float(sv[h][c + 1]), sl2, -ms));
+        sum4[j & 3] += p0 + p1;
         pk[j] = pack2(p0, p1);  // element 2j in the low half, 2j+1 in the high half
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run = l_run * corr + sum;
       if (it > 0) {
         // O of the tiles so far must be complete (and P of the last tile consumed) before either
@@ -270,7 +294,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           }
         }
       }
-      tmem_st32(lane_base + COL_P, pk);
+      tmem_st32(s_buf, pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
@@ -342,7 +366,7 @@ inline int launch_prefill(const LseAttnArgs* a, long long total_rows, long long 
   p.page_shift = 0;
   while ((1 << p.page_shift) < a->page_tokens) ++p.page_shift;
   p.error_flag = error_flag;
-  constexpr int smem = Q_BYTES + 2 * STAGES * KV_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+  constexpr int smem = Q_BYTES + 2 * STAGES * KV_BYTES + (2 * STAGES + 5) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
@@ -350,7 +374,7 @@ inline int launch_prefill(const LseAttnArgs* a, long long total_rows, long long 
       return LSE_LAUNCH_FAILED;
     configured = true;
   }
-  dim3 grid(a->num_tiles, a->num_heads);
+  dim3 grid(a->num_heads, a->num_tiles);
   return lse::launch(prefill_tc_kernel, grid, THREADS, smem, stream, mq, mk, mv, p) == cudaSuccess
              ? LSE_OK
              : LSE_LAUNCH_FAILED;

@@ -403,14 +403,14 @@ extern "C" int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bi
   p.bias = reinterpret_cast<const bf16*>(bias); p.error_flag = error_flag;
   const long long units = (long long)p.tiles * p.chunks;
   // two blocks per SM (five stages each fit twice in shared memory) keep more copies in flight
-  const int per_sm = nt <= 32 ? 2 : 1;
+  const int per_sm = nt <= 64 ? 2 : 1;
   int grid = tc::sm_count() * per_sm;
   if (p.whole_tiles) grid = grid < p.tiles ? grid : p.tiles;
   else if (units < grid) grid = (int)units;
   switch (nt) {
     case 16: return tc::launch<16, 5>(mw, ma, p, grid, stream);
     case 32: return tc::launch<32, 5>(mw, ma, p, grid, stream);
-    case 64: return tc::launch<64, 8>(mw, ma, p, grid, stream);
+    case 64: return tc::launch<64, 4>(mw, ma, p, grid, stream);
     case 128: return tc::launch<128, 6>(mw, ma, p, grid, stream);
     default: return tc::launch<256, 4>(mw, ma, p, grid, stream);
   }

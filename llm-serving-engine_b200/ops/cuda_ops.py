@@ -34,7 +34,7 @@ class CudaOps:
         self.attention_kernel = 0  # 0: fastest available; 1: CUDA cores; 2: mma.sync (tests compare them)
         self.use_skinny_gemm = True
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
-        self.skinny_atomic_rows = 64  # above this the atomics' traffic is no longer small
+        self.skinny_atomic_rows = 32  # measured: above this the library's kernels are faster
         # float32 accumulation buffers of the few-rows product, by shape. Invariant: a buffer that
         # is not in _ws_live reads as zero (the kernel that consumes a product zeroes what it reads).
         self._addmm_in_place: bool | None = None  # whether torch.addmm can add into a float32 tensor

@@ -17,10 +17,8 @@
 //
 // Every wait on an mbarrier is bounded: on expiry the block records an error code in *error_flag
 // and leaves through the normal teardown (tensor memory is released).
-#include <cuda.h>
-
-#include "common.cuh"
 #include "kernels.h"
+#include "tma_util.cuh"
 
 namespace lse {
 namespace tc {
@@ -28,58 +26,9 @@ namespace tc {
 constexpr int BM = 128;        // output features per block (MMA M)
 constexpr int BK = 64;         // k elements per stage: 128 bytes, one swizzle row
 constexpr int UMMA_K = 16;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-// Bounded wait. Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar,
-                                            int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
-      "%4}], [%2];"
-      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows of 128 bytes, groups of
-// 8 rows 1024 bytes apart (tile base aligned to 1024 bytes).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);   // start address
-  d |= (uint64_t)1 << 16;                   // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
-  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M x N.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
+using namespace tma;
+
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc,
                                      uint32_t accumulate) {
   asm volatile(
@@ -87,11 +36,6 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               ::"r"(smem_u32(bar))
-               : "memory");
 }
 
 struct Params {
@@ -214,7 +158,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else if (my_units > 0 && warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer
-      constexpr uint32_t idesc = instr_desc(BM, NT);
+      constexpr uint32_t idesc = instr_desc_bf16(BM, NT);
       int it = 0, seg = 0;
       while (it < my_units && !failed) {
         const long long u0 = u_begin + it;
@@ -233,8 +177,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           ok = mbar_wait(&full[s], (it / STAGES) & 1);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da = smem_desc(smem_u32(w_tiles + s * W_BYTES));
-          const uint64_t db = smem_desc(smem_u32(a_tiles + s * A_BYTES));
+          const uint64_t da = smem_desc_sw128(smem_u32(w_tiles + s * W_BYTES));
+          const uint64_t db = smem_desc_sw128(smem_u32(a_tiles + s * A_BYTES));
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             // 16 k-elements = 32 bytes further along the swizzled row: +2 in the address field
@@ -320,36 +264,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 }
 
 // ---------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// [rows, K] bfloat16 row-major; box = [box_rows, 64 k]; rows or k past the edge read as zero.
-static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int NT, int STAGES>
 static int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Params& p, int grid,
                   cudaStream_t stream) {
@@ -393,7 +307,7 @@ extern "C" int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bi
   if (atomic_add && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
   const int nt = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
   CUtensorMap mw, ma;
-  if (!tc::make_map(&mw, w, N, K, tc::BM) || !tc::make_map(&ma, a, T, K, nt)) return LSE_LAUNCH_FAILED;
+  if (!tma::make_map_bf16(&mw, w, N, K, K, tc::BM) || !tma::make_map_bf16(&ma, a, T, K, K, nt)) return LSE_LAUNCH_FAILED;
   tc::Params p;
   p.T = T; p.N = N; p.K = K;
   p.tiles = (N + tc::BM - 1) / tc::BM;

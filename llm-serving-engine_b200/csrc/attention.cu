@@ -405,7 +405,6 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   __shared__ float sm_m[DEC_WARPS][GT], sm_l[DEC_WARPS][GT];
   __shared__ float sm_acc[DEC_WARPS][GT][D];
   pdl_trigger();
-  pdl_wait();
 
   const int split = blockIdx.x, b = blockIdx.z;
   const int G = a.num_heads / a.num_kv_heads;
@@ -428,6 +427,10 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   const T* kp = (const T*)a.k_pages;
   const T* vp = (const T*)a.v_pages;
 
+  // The batch description is an input of the step, not a result of earlier kernels, so the index
+  // arithmetic above runs before the dependency wait.
+  pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
+
   float qreg[GT][CPL][VEC], acc[GT][CPL][VEC], m[GT], l[GT];
 #pragma unroll
   for (int gq = 0; gq < GT; ++gq) {
@@ -437,9 +440,11 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
 #pragma unroll
     for (int c = 0; c < CPL; ++c) {
       const int ch = li + c * LPK;
+      Vec16<T> qv;
+      if (ch < NCHUNK) qv = load16(q + ch * VEC);
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        qreg[gq][c][e] = ch < NCHUNK ? Num<T>::to_float(q[ch * VEC + e]) * a.scale : 0.f;
+        qreg[gq][c][e] = ch < NCHUNK ? Num<T>::to_float(qv.v[e]) * a.scale : 0.f;
         acc[gq][c][e] = 0.f;
       }
     }

@@ -62,7 +62,9 @@ class _Graph:
         so = self.off["seed"]
         self.sample_args = (f32("temperature"), view("top_k"), f32("top_p"), f32("min_p"),
                             self.dev[so : so + 2 * B].view(torch.int64), view("draw"))
-        self.tokens_host = torch.zeros(B, dtype=torch.int32).pin_memory()
+        self.tokens_host = [torch.zeros(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.turn = 0
+        self.h2d_done: torch.cuda.Event | None = None  # the pinned input buffer may be rewritten after it
         self.graph: torch.cuda.CUDAGraph | None = None
         self.tokens: torch.Tensor | None = None
         self.launches = 0
@@ -99,14 +101,17 @@ class DecodeGraphs:
                 return False
         return True
 
-    def _fill(self, g: _Graph, entries, rows) -> int:
+    def _fill(self, g: _Graph, entries, rows, ahead: int = 0) -> int:
+        """Write the step's inputs into the pinned buffer. ``ahead`` = 1 describes the step *after*
+        one that is still running: every position is one further and the token ids are not known
+        on the host (they are copied on the device from that step's samples)."""
         m = self.runner.manager
         B = g.batch
         tok, pos, ctx = g.hview("token_ids"), g.hview("positions"), g.hview("ctx_lens")
         slots, first = g.hview("state_slots"), g.hview("first_portion")
         for i, e in enumerate(entries):
             held = m.held[e.rid]
-            c = held.computed
+            c = held.computed + ahead
             tok[i] = e.tokens[0]
             pos[i] = c
             ctx[i] = c + 1
@@ -135,7 +140,7 @@ class DecodeGraphs:
         g.hview("top_k")[:] = [q.top_k for q in p]
         g.hview("top_p", np.float32)[:] = [q.top_p for q in p]
         g.hview("min_p", np.float32)[:] = [q.min_p for q in p]
-        g.hview("draw")[:] = [len(r.output_token_ids) for r in rows]
+        g.hview("draw")[:] = [r.draw_index for r in rows]
         so = g.off["seed"]
         g.h[so : so + 2 * B].view(np.uint64)[:] = [r.seed & 0xFFFFFFFFFFFFFFFF for r in rows]
         return int(ctx.max())
@@ -163,22 +168,52 @@ class DecodeGraphs:
             g.tokens = self._forward(g)
         g.launches = ops.launches - before
 
-    def run(self, entries: Sequence[StepEntry], rows) -> list[int]:
+    def launch(self, entries: Sequence[StepEntry], rows, ahead_of: "Pending | None" = None) -> "Pending":
+        """Enqueue a step (inputs copy, graph replay, token read-back) without waiting for it.
+
+        With ``ahead_of`` the step continues the same sequences one position after that still
+        running step and takes its input token ids on the device from that step's samples.
+        """
         runner = self.runner
         B = len(entries)
-        max_ctx = 1 + max(runner.manager.held[e.rid].computed for e in entries)
+        ahead = 0 if ahead_of is None else 1
+        max_ctx = 1 + ahead + max(runner.manager.held[e.rid].computed for e in entries)
         splits = runner.ops.decode_splits(B, self.min_kv_heads, max_ctx)
         key = (B, splits)
         g = self.graphs.get(key)
         if g is None:
             g = self.graphs[key] = _Graph(self, B, splits)
-        self._fill(g, entries, rows)
+        if g.h2d_done is not None:
+            g.h2d_done.synchronize()
+        self._fill(g, entries, rows, ahead)
         g.dev.copy_(g.host, non_blocking=True)
+        g.h2d_done = torch.cuda.Event()
+        g.h2d_done.record()
+        if ahead_of is not None:
+            g.step.token_ids.copy_(ahead_of.graph.tokens, non_blocking=True)
         if g.graph is None:
             self._capture(g)
         g.graph.replay()
         runner.ops.launches += g.launches
-        g.tokens_host.copy_(g.tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        buf = g.tokens_host[g.turn]
+        g.turn ^= 1
+        buf.copy_(g.tokens, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
         runner.steps_run += 1
-        return g.tokens_host.tolist()
+        return Pending(g, done, buf)
+
+    @staticmethod
+    def collect(pending: "Pending") -> list[int]:
+        pending.done.synchronize()
+        return pending.tokens_host.tolist()
+
+    def run(self, entries: Sequence[StepEntry], rows) -> list[int]:
+        return self.collect(self.launch(entries, rows))
+
+
+class Pending:
+    """A launched step whose sampled tokens have not been read yet."""
+
+    def __init__(self, graph: _Graph, done, tokens_host) -> None:
+        self.graph, self.done, self.tokens_host = graph, done, tokens_host

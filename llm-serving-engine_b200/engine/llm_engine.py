@@ -37,6 +37,7 @@ class EngineConfig:
     enable_prefix_caching: bool = False  # not built: pages are reused, their contents are not
     seed: int = 0  # weights seed of "random:<alias>" models
     cuda_graphs: bool = True  # replay captured graphs for steps of single tokens only
+    run_ahead: bool = True  # launch the next decode step before this one's tokens are read
     config_overrides: dict | None = None  # config.json keys to replace in a "random:<alias>" model
 
     def scheduler_config(self) -> SchedulerConfig:
@@ -46,6 +47,18 @@ class EngineConfig:
             enable_chunked_prefill=self.enable_chunked_prefill,
             max_model_len=self.max_model_len,
         )
+
+
+class _InFlight:
+    """A step that has been launched: who was scheduled, and the handle or result of the GPU work."""
+
+    def __init__(self, scheduled, sample_seqs, stats, t0) -> None:
+        self.scheduled = scheduled  # [(sequence, new tokens)]
+        self.sample_seqs = sample_seqs
+        self.stats = stats
+        self.t0 = t0
+        self.pending = None  # handle of a launched CUDA-graph step
+        self.result = None  # SamplerOutput of a step that ran synchronously
 
 
 @dataclass
@@ -116,6 +129,7 @@ class LLMEngine:
             self.eos_ids.add(tokenizer.eos_token_id)
         self.last_step = StepStats()
         self.total_steps = 0
+        self._pending: _InFlight | None = None  # a step launched ahead, not yet collected
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt: str | list[int], params: SamplingParams | None = None,
@@ -169,13 +183,39 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ step
     def step(self) -> list[RequestOutput]:
+        """One engine iteration: returns the outputs of the step it completes.
+
+        Steps of single tokens are launched as CUDA graphs without waiting. Before the tokens of
+        such a step are read, the step after it is launched *ahead* when nothing can change the
+        batch in between (nobody can finish by length, nobody waits, pages are there): its input
+        token ids are copied on the device from the running step's samples. So the host's work
+        (reading tokens, stop checks, outputs, preparing inputs) overlaps the GPU's. If a sequence
+        does end (EOS, stop token, abort), the step launched ahead is dropped; what it wrote lies
+        beyond every live sequence's committed tokens and is never read.
+        """
+        cur = self._pending
+        self._pending = None
+        if cur is not None and all(seq.is_finished for seq, _ in cur.scheduled):
+            self.runner.collect_decode(cur.pending)  # every sequence of it was aborted: nothing to keep
+            cur = None
+        if cur is None:
+            cur = self._start_step()
+            if cur is None:
+                return []
+        ahead = self._launch_ahead(cur)
+        outputs, unchanged = self._finish_step(cur)
+        if ahead is not None and unchanged:
+            self._pending = ahead
+        return outputs
+
+    def _start_step(self):
         t0 = time.monotonic()
         sched = self.scheduler.schedule()
         t1 = time.monotonic()
         stats = StepStats(num_preempted=len(sched.preempted), t_schedule=t1 - t0)
         if sched.is_empty:
             self.last_step = stats
-            return []
+            return None
         # Sequences that reach the end of their known tokens this step get a new token
         # (src/llmserve/engine.py:323-332); the others are in the middle of a prompt.
         entries, sample_seqs = [], []
@@ -187,28 +227,75 @@ class LLMEngine:
             if last:
                 sample_seqs.append(seq)
         rows = [self._sample_row(seq) for seq in sample_seqs]
-        out = self.runner.step_and_sample(entries, self.sampler, rows, graphs=self.cfg.cuda_graphs)
-        t2 = time.monotonic()
-        stats.t_forward = t2 - t1
-        for s in sched.scheduled:
-            self.manager.commit(s.seq.seq_id, s.num_new_tokens)
-            s.seq.num_computed_tokens += s.num_new_tokens
-            if s.num_new_tokens == 1 and s.seq.output_token_ids:
+        scheduled = [(s.seq, s.num_new_tokens) for s in sched.scheduled]
+        flight = _InFlight(scheduled, sample_seqs, stats, t0)
+        if self.cfg.cuda_graphs and self.runner.can_launch_decode(entries, rows):
+            flight.pending = self.runner.launch_decode(entries, rows)
+        else:
+            flight.result = self.runner.step_and_sample(entries, self.sampler, rows, graphs=False)
+        return flight
+
+    def _launch_ahead(self, cur: "_InFlight"):
+        """Launch the step after ``cur`` before ``cur``'s tokens are known, if the batch cannot change."""
+        if cur.pending is None or not self.cfg.run_ahead or self.scheduler.waiting:
+            return None
+        seqs = cur.sample_seqs
+        if len(seqs) != len(cur.scheduled) or len(seqs) != len(self.scheduler.running):
+            return None
+        if len(seqs) > self.cfg.max_num_batched_tokens:
+            return None
+        for seq in seqs:
+            p = seq.params
+            if (seq.is_finished or len(seq.output_token_ids) + 1 >= p.max_tokens
+                    or seq.num_tokens + 1 >= self.cfg.max_model_len
+                    or not self.manager.can_allocate(seq.seq_id, 2)):
+                return None
+        rows = [self._sample_row(seq, ahead=1) for seq in seqs]
+        entries = [StepEntry(seq.seq_id, [0], [0]) for seq in seqs]
+        if not self.runner.can_launch_decode(entries, rows):
+            return None
+        for seq in seqs:
+            self.manager.allocate(seq.seq_id, 2)
+        t0 = time.monotonic()
+        flight = _InFlight([(seq, 1) for seq in seqs], list(seqs), StepStats(), t0)
+        flight.pending = self.runner.launch_decode(entries, rows, ahead_of=cur.pending)
+        return flight
+
+    def _finish_step(self, cur: "_InFlight"):
+        """Read the step's tokens and do the host's part. Returns (outputs, batch unchanged)."""
+        stats = cur.stats
+        t1 = time.monotonic()
+        if cur.pending is not None:
+            tokens = self.runner.collect_decode(cur.pending)
+            logprobs = tops = None
+        else:
+            tokens, logprobs, tops = cur.result.token_ids, cur.result.logprobs, cur.result.top_logprobs
+        stats.t_forward = time.monotonic() - t1
+        unchanged = True
+        for seq, n in cur.scheduled:
+            if seq.is_finished:  # aborted while the step ran
+                unchanged = False
+                continue
+            self.manager.commit(seq.seq_id, n)
+            seq.num_computed_tokens += n
+            if n == 1 and seq.output_token_ids:
                 stats.num_decode_tokens += 1
             else:
-                stats.num_prefill_tokens += s.num_new_tokens
+                stats.num_prefill_tokens += n
         now = time.monotonic()
         touched: dict[str, Request] = {}
-        for j, seq in enumerate(sample_seqs):
-            self._append_token(
-                seq, out.token_ids[j],
-                None if out.logprobs is None else out.logprobs[j],
-                None if out.top_logprobs is None else out.top_logprobs[j], now)
+        for j, seq in enumerate(cur.sample_seqs):
+            if seq.is_finished:
+                continue
+            self._append_token(seq, tokens[j], None if logprobs is None else logprobs[j],
+                               None if tops is None else tops[j], now)
             touched[seq.request.request_id] = seq.request
-        stats.num_seqs = len(sched.scheduled)
-        stats.num_tokens = sched.num_tokens
-        stats.step_time = time.monotonic() - t0
-        stats.t_postprocess = stats.step_time - stats.t_schedule - stats.t_forward
+            if seq.is_finished:
+                unchanged = False
+        stats.num_seqs = len(cur.scheduled)
+        stats.num_tokens = sum(n for _, n in cur.scheduled)
+        stats.step_time = time.monotonic() - cur.t0
+        stats.t_postprocess = time.monotonic() - now
         self.last_step = stats
         self.total_steps += 1
         outputs = []
@@ -217,14 +304,17 @@ class LLMEngine:
             if req.is_finished:
                 req.metrics.finished_time = now
                 self.requests.pop(req.request_id, None)
-        return outputs
+        return outputs, unchanged
 
-    def _sample_row(self, seq: Sequence) -> SampleRow:
+    def _sample_row(self, seq: Sequence, ahead: int = 0) -> SampleRow:
+        """``ahead`` = 1: the row of the token *after* the one that is being sampled right now."""
         p = seq.params
+        n_out = len(seq.output_token_ids) + ahead
         banned = []
-        if len(seq.output_token_ids) < p.min_tokens:
+        if n_out < p.min_tokens:
             banned = sorted(self.eos_ids | set(p.stop_token_ids))
-        return SampleRow(p, seq.output_token_ids, seq.prompt_token_ids, seq.seed, banned)
+        return SampleRow(p, seq.output_token_ids, seq.prompt_token_ids, seq.seed, banned,
+                         draw=n_out if ahead else None)
 
     def _append_token(self, seq, token, logprob, top, now) -> None:
         req = seq.request

@@ -192,6 +192,26 @@ class ModelRunner:
         """Give back everything ``rid`` holds."""
         self.manager.release(rid)
 
+    def can_launch_decode(self, entries: Sequence[StepEntry], rows) -> bool:
+        from .decode_graph import DecodeGraphs
+
+        return self.device.type == "cuda" and DecodeGraphs.usable(entries, rows)
+
+    def launch_decode(self, entries: Sequence[StepEntry], rows, ahead_of=None):
+        """Enqueue a step of single tokens as a CUDA graph and return without waiting for it
+        (see :meth:`DecodeGraphs.launch`); :meth:`collect_decode` waits and returns the tokens."""
+        from .decode_graph import DecodeGraphs
+
+        if self.decode_graphs is None:
+            self.decode_graphs = DecodeGraphs(self)
+        pending = self.decode_graphs.launch(entries, rows, ahead_of)
+        self.last_h2d_bytes = 4 * pending.graph.words
+        self.last_d2h_bytes = 4 * len(entries)
+        return pending
+
+    def collect_decode(self, pending) -> list[int]:
+        return self.decode_graphs.collect(pending)
+
     def step_and_sample(self, entries: Sequence[StepEntry], sampler, rows, graphs: bool = False):
         """A step followed by sampling on the device; only token ids come back to the host.
 

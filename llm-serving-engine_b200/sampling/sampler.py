@@ -29,6 +29,11 @@ class SampleRow:
     prompt_token_ids: list[int]
     seed: int  # the request's 64-bit seed
     banned_token_ids: list[int] = field(default_factory=list)  # e.g. EOS before min_tokens
+    draw: int | None = None  # index of the token being generated, if not len(output_token_ids)
+
+    @property
+    def draw_index(self) -> int:
+        return len(self.output_token_ids) if self.draw is None else self.draw
 
 
 @dataclass
@@ -101,7 +106,7 @@ class Sampler:
             self._dev([q.top_p for q in p], torch.float32),
             self._dev([q.min_p for q in p], torch.float32),
             self._dev([_as_int64(r.seed) for r in rows], torch.int64),
-            self._dev([len(r.output_token_ids) for r in rows], torch.int32),
+            self._dev([r.draw_index for r in rows], torch.int32),
         )
         if not want_lp:
             return SamplerOutput(tokens.tolist(), None, None)

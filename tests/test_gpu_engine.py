@@ -85,6 +85,55 @@ def test_long_generation_with_graphs_matches_stepwise(sharp_dirs):
     assert a[0].outputs[0].token_ids == plain_llama.greedy(sharp_dirs["C"], PROMPTS[0], 120)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_ahead_changes_nothing(sharp_dirs, dtype):
+    """Steps launched before the last one's tokens are read: same tokens, also when sequences stop
+    at different times (stop tokens), which drops a step that was launched ahead."""
+    from llmserve_b200 import SamplingParams
+
+    free = plain_llama.greedy(sharp_dirs["A"], PROMPTS[0], 30)
+    stop = next(t for i, t in enumerate(free) if i >= 9 and t not in free[:i])  # first met late
+    params = [SamplingParams(temperature=0.0, max_tokens=30, stop_token_ids=[stop]),
+              SamplingParams(temperature=0.0, max_tokens=17, ignore_eos=True),
+              SamplingParams(temperature=0.9, top_k=40, seed=5, max_tokens=25, ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)]
+    outs = {}
+    for ahead in (False, True):
+        m = llm(sharp_dirs["A"], "A", dtype, run_ahead=ahead)
+        res = m.generate(PROMPTS[:4], params)
+        outs[ahead] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason) for o in res]
+        m.engine.manager.check_invariants()
+        assert m.engine.manager.usage() == 0.0
+    if dtype == "float32":
+        assert outs[True] == outs[False]
+        assert outs[True][0][0] == free[: free.index(stop) + 1] and outs[True][0][1] == "stop"
+    else:  # bfloat16 sums are order-dependent (atomics): lengths and reasons must still agree
+        assert [(len(t), r) for t, r in outs[True][1:]] == [(len(t), r) for t, r in outs[False][1:]]
+    assert [len(t) for t, _ in outs[True]][1:] == [17, 25, 30]
+
+
+def test_abort_while_a_step_is_in_flight(sharp_dirs):
+    from llmserve_b200 import SamplingParams
+
+    m = llm(sharp_dirs["B"], "B", "float32")
+    eng = m.engine
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    a = eng.add_request(PROMPTS[0], sp)
+    b = eng.add_request(PROMPTS[1], sp)
+    for _ in range(6):
+        eng.step()
+    assert eng._pending is not None  # a step was launched ahead
+    eng.abort_request(a)
+    done = {}
+    while eng.has_unfinished_requests():
+        for o in eng.step():
+            if o.finished:
+                done[o.request_id] = o
+    assert done[b].outputs[0].token_ids == plain_llama.greedy(sharp_dirs["B"], PROMPTS[1], 40)
+    eng.manager.check_invariants()
+    assert eng.manager.usage() == 0.0
+
+
 def test_cli_generates(sharp_dirs, capsys):
     from llmserve_b200.cli import main
 

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import BLOCKS, NORMS, BuildEnv, ParamDecl, role_dtype
+from ..parts.base import BLOCKS, NORMS, POSITION_ENCODINGS, BuildEnv, ParamDecl, role_dtype
 from .plan import ModelPlan
 
 
@@ -21,6 +21,9 @@ class DecoderModel:
         self.ops = env.ops
         self.blocks = [BLOCKS.build(spec, env) for spec in plan.layers]
         self.final_norm = NORMS.build(plan.final_norm, env)
+        self.embed_position = (
+            POSITION_ENCODINGS.build(plan.embed_position, env) if plan.embed_position is not None else None
+        )
         self.embed_weight: torch.Tensor | None = None
         self.head_weight: torch.Tensor | None = None
         # which run of the order fills each cache layer
@@ -98,6 +101,8 @@ class DecoderModel:
     def forward(self, step, pools) -> torch.Tensor:
         """Run this step's tokens; return float32 logits ``[len(step.logit_rows), vocab]``."""
         x = self.ops.embedding(step.token_ids, self.embed_weight)
+        if self.embed_position is not None:
+            self.embed_position.embed(x, step.positions)  # absolute encodings change x in place
         pending = None
         for k, e in enumerate(self.plan.run_order):
             view = pools.view(e.cache, writes=self.writer_of[e.cache] == k)

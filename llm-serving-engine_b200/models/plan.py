@@ -28,6 +28,7 @@ class ModelPlan:
     run_order: tuple[RunEntry, ...]
     final_norm: Any  # norm spec
     tie_head: bool
+    embed_position: Any = None  # position-encoding spec applied to the embedded tokens, or None
 
     def validate(self) -> None:
         if not self.run_order:

@@ -161,3 +161,198 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tiny_dirs):
     expected = {r: toy_plain(w, pcfg, t, 0.9, mix_w) for r, t in reqs.items()}
     got = traces.replay(runner, traces.mixed(reqs, seed=4))  # slots are handed out again
     traces.compare(got, expected, atol=2e-5)
+
+
+# ------------------------------------------------------------------ the attention part and the block alone
+def test_attention_part_and_block_alone(tiny_dirs):
+    """One PagedAttention part, then one PreNormBlock, built from specs and stepped on a ragged batch."""
+    from llmserve_b200.cache import CacheManager, CachePools, KVGroupSpec
+    from llmserve_b200.engine.batch import StepEntry, build_host_step
+    from llmserve_b200.engine.runner import ModelRunner
+    from llmserve_b200.ops import get_ops
+    from llmserve_b200.parts import (BLOCKS, MIXERS, AttentionSpec, BuildEnv, PreNormBlockSpec,
+                                     RMSNormSpec, RotarySpec, SwiGLUSpec)
+
+    H, nq, nk, D, I, page = 96, 6, 3, 16, 200, 8
+    env = BuildEnv(get_ops("cuda"), torch.float32, torch.device("cuda"), 64, torch.float32)
+    aspec = AttentionSpec(H, nq, nk, D, D**-0.5, RotarySpec(D, 777.0), bias=True)
+    bspec = PreNormBlockSpec(RMSNormSpec(H, 1e-5), aspec, RMSNormSpec(H, 2e-6), SwiGLUSpec(H, I))
+    block = BLOCKS.build(bspec, env)
+    g = torch.Generator().manual_seed(0)
+    w = {n: (torch.randn(d.shape, generator=g) * (0.1 if d.role != "scale" else 0.05) + (d.role == "scale"))
+         for n, d in block.param_decls().items()}
+    block.bind({n: t.cuda() for n, t in w.items()})
+    # the plain model's names for the same tensors
+    q, kv = nq * D, nk * D
+    pw = {"a.q_proj.weight": w["mixer.qkv.weight"][:q], "a.k_proj.weight": w["mixer.qkv.weight"][q : q + kv],
+          "a.v_proj.weight": w["mixer.qkv.weight"][q + kv :], "a.q_proj.bias": w["mixer.qkv.bias"][:q],
+          "a.k_proj.bias": w["mixer.qkv.bias"][q : q + kv], "a.v_proj.bias": w["mixer.qkv.bias"][q + kv :],
+          "a.o_proj.weight": w["mixer.o.weight"], "a.o_proj.bias": w["mixer.o.bias"]}
+    cfg = dict(heads=nq, kv_heads=nk, head_dim=D, theta=777.0, rope_scaling=None, bias=True)
+    lens = [19, 1, 30]
+    xs = [torch.randn(n, H, generator=g) for n in lens]
+    manager = CacheManager([KVGroupSpec((0,), nk, D, 0, page)], [16], 4)
+    pools = CachePools(manager.groups, [], [16], 4, torch.float32, "cuda")
+    for i, n in enumerate(lens):
+        manager.admit(i)
+        manager.allocate(i, n)
+    host = build_host_step([StepEntry(i, [0] * n, []) for i, n in enumerate(lens)], manager, 10, 64)
+    # reuse the runner's upload by hand: a DeviceStep needs the attention plan of this mixer
+    runner = ModelRunner.__new__(ModelRunner)
+    runner.device, runner.pools, runner._staging, runner._staging_turn = env.device, pools, [], 0
+    runner.planners = {block.mixer.plan_key(): (block.mixer, 0)}
+    runner.last_h2d_bytes = 0
+    step = runner.upload(host)
+    x = torch.cat(xs).cuda()
+    x_in = x.clone()
+    x_out, pending = block.forward(x, None, step, pools.view(0, writes=True))
+    got = (x_out if pending is None else x_out + pending.float()).cpu()
+    # plain: per sequence, whole
+    want = []
+    for xi in xs:
+        h = plain_llama.rms_norm(xi, w["norm_in.weight"], 1e-5)
+        a, _ = plain_llama.attention_block(h, pw, "a.", cfg, torch.arange(xi.shape[0]))
+        y = xi + a
+        h = plain_llama.rms_norm(y, w["norm_post.weight"], 2e-6)
+        want.append(y + plain_llama.swiglu(h, w["feed_forward.gate_up.weight"][:I],
+                                           w["feed_forward.gate_up.weight"][I:], w["feed_forward.down.weight"]))
+    assert (got - torch.cat(want)).abs().max() < 2e-5
+    # the mixer alone, on the block's first norm output
+    mixer = MIXERS.build(aspec, env)
+    mixer.bind({k[len("mixer."):]: v.cuda() for k, v in w.items() if k.startswith("mixer.")})
+    h = block.norm_in.forward(x_in.clone(), None)
+    a = mixer.forward(h, step, pools.view(0, writes=True)).cpu()
+    ref = torch.cat([plain_llama.attention_block(plain_llama.rms_norm(xi, w["norm_in.weight"], 1e-5), pw, "a.", cfg,
+                                                 torch.arange(xi.shape[0]))[0] for xi in xs])
+    assert (a - ref).abs().max() < 2e-5
+
+
+# ------------------------------------------------------------------ toy feed-forward with routing, toy positions
+@dataclass(frozen=True)
+class TopOneSpec:
+    hidden_size: int
+    inner: int
+    experts: int
+    kind: str = "toy_top1"
+
+
+@dataclass(frozen=True)
+class SinusoidSpec:
+    hidden_size: int
+    base: float
+    kind: str = "toy_sinusoid"
+
+
+def register_toy_ffn_and_positions():
+    from llmserve_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, ParamDecl, PositionEncoding
+
+    if "toy_top1" not in FEED_FORWARDS.classes:
+        @FEED_FORWARDS.register("toy_top1")
+        class TopOne(FeedForward):
+            """Router logits in float32, one expert per token: y = relu(h W1_e) W2_e * p_e."""
+
+            def param_decls(self):
+                s = self.spec
+                d = {"router.weight": ParamDecl((s.experts, s.hidden_size), "matrix")}
+                for e in range(s.experts):
+                    d[f"w1.{e}.weight"] = ParamDecl((s.inner, s.hidden_size), "matrix")
+                    d[f"w2.{e}.weight"] = ParamDecl((s.hidden_size, s.inner), "matrix")
+                return d
+
+            def bind(self, params):
+                self.p = params
+
+            def forward(self, h, step):
+                logits = self.ops.linear(h, self.p["router.weight"], None, out_dtype=torch.float32)
+                prob, pick = logits.softmax(-1).max(-1)
+                out = torch.zeros(h.shape[0], self.spec.hidden_size, dtype=torch.float32, device=h.device)
+                for e in range(self.spec.experts):
+                    rows = (pick == e).nonzero()[:, 0]
+                    if rows.numel():
+                        a = torch.relu(self.ops.linear(h[rows].contiguous(), self.p[f"w1.{e}.weight"], None,
+                                                       out_dtype=torch.float32))
+                        out[rows] = self.ops.linear(a.contiguous(), self.p[f"w2.{e}.weight"], None,
+                                                    out_dtype=torch.float32) * prob[rows, None]
+                return out
+
+    if "toy_sinusoid" not in POSITION_ENCODINGS.classes:
+        @POSITION_ENCODINGS.register("toy_sinusoid")
+        class Sinusoid(PositionEncoding):
+            """Absolute positions added to the embedded tokens (the ``embed`` hook)."""
+
+            def __init__(self, spec, env):
+                super().__init__(spec, env)
+                self.table = sinusoid_table(env.max_positions, spec.hidden_size, spec.base).to(env.device)
+
+            def embed(self, x, positions):
+                x += self.table[positions.long()]
+
+
+def sinusoid_table(n, width, base):
+    pos = torch.arange(n, dtype=torch.float64)[:, None]
+    freq = base ** (-torch.arange(0, width, 2, dtype=torch.float64) / width)
+    return torch.cat([(pos * freq).sin(), (pos * freq).cos()], dim=-1).float()
+
+
+def test_toy_routed_feed_forward_and_absolute_positions(tiny_dirs):
+    """Another feed-forward (routing) in layer 1 and another position encoding (absolute, added at
+    the embedding; the attention layers then use none), registered here and stepped in every cut."""
+    from llmserve_b200.config import load_model_config
+    from llmserve_b200.engine.runner import ModelRunner
+    from llmserve_b200.models import DecoderModel
+    from llmserve_b200.ops import get_ops
+    from llmserve_b200.parts import BuildEnv, NoPositionSpec
+    from llmserve_b200.weights import load_parameters
+
+    register_toy_ffn_and_positions()
+    folder = tiny_dirs["A"]
+    arch, cfg = load_model_config(folder)
+    plan = arch.plan(cfg)
+    H = cfg.hidden_size
+    nopos = [dataclasses.replace(l, mixer=dataclasses.replace(l.mixer, position=NoPositionSpec())) for l in plan.layers]
+    routed = dataclasses.replace(nopos[1], feed_forward=TopOneSpec(H, 48, 3))
+    plan = dataclasses.replace(plan, layers=(nopos[0], routed), embed_position=SinusoidSpec(H, 50.0))
+    env = BuildEnv(get_ops("cuda"), torch.float32, torch.device("cuda"), 256, torch.float32)
+    model = DecoderModel(plan, env)
+    params = load_parameters(folder, arch.checkpoint_layout(cfg), torch.float32, "cuda")
+    params = {k: v for k, v in params.items() if not k.startswith("layers.1.feed_forward.")}
+    g = torch.Generator().manual_seed(3)
+    toy = {}
+    for name, d in model.param_decls().items():
+        if name.startswith("layers.1.feed_forward."):
+            toy[name] = torch.randn(d.shape, generator=g) * (1.0 if "router" in name else 0.08)
+    model.bind({**params, **{k: v.cuda() for k, v in toy.items()}})
+    runner = ModelRunner(model, page_tokens=16, num_pages=24, max_model_len=256, max_num_seqs=4)
+    reqs = traces.make_requests([40, 23, 70, 9, 55], 256, seed=17)
+    pcfg, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)
+    table = sinusoid_table(256, H, 50.0)
+
+    def plain(ids):
+        T = len(ids)
+        x = w["model.embed_tokens.weight"][torch.as_tensor(ids)] + table[:T]
+        for layer in range(2):
+            p = f"model.layers.{layer}."
+            h = plain_llama.rms_norm(x, w[p + "input_layernorm.weight"], pcfg["eps"])
+            qq = (h @ w[p + "self_attn.q_proj.weight"].T).view(T, pcfg["heads"], pcfg["head_dim"])
+            kk = (h @ w[p + "self_attn.k_proj.weight"].T).view(T, pcfg["kv_heads"], pcfg["head_dim"])
+            vv = (h @ w[p + "self_attn.v_proj.weight"].T).view(T, pcfg["kv_heads"], pcfg["head_dim"])
+            a = plain_llama.attention(qq, kk, vv, pcfg["head_dim"] ** -0.5).reshape(T, -1)
+            x = x + a @ w[p + "self_attn.o_proj.weight"].T
+            h = plain_llama.rms_norm(x, w[p + "post_attention_layernorm.weight"], pcfg["eps"])
+            if layer == 0:
+                x = x + plain_llama.swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                                           w[p + "mlp.down_proj.weight"])
+            else:
+                prob, pick = (h @ toy["layers.1.feed_forward.router.weight"].T).softmax(-1).max(-1)
+                y = torch.zeros_like(x)
+                for e in range(3):
+                    rows = pick == e
+                    a1 = torch.relu(h[rows] @ toy[f"layers.1.feed_forward.w1.{e}.weight"].T)
+                    y[rows] = (a1 @ toy[f"layers.1.feed_forward.w2.{e}.weight"].T) * prob[rows, None]
+                x = x + y
+        x = plain_llama.rms_norm(x, w["model.norm.weight"], pcfg["eps"])
+        return x @ w["model.embed_tokens.weight"].T
+
+    expected = {r: plain(t) for r, t in reqs.items()}
+    got = traces.replay(runner, traces.mixed(reqs, seed=6))
+    traces.compare(got, expected, atol=3e-5)

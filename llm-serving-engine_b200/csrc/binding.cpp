@@ -27,6 +27,9 @@ int dtype_code(const Tensor& t, const char* what) {
 void check_cuda(const Tensor& t, const char* what) {
   TORCH_CHECK(t.is_cuda(), what, " must be a CUDA tensor");
   TORCH_CHECK(t.is_contiguous(), what, " must be contiguous");
+  // the kernels read and write 16-byte vectors wherever a row holds whole ones
+  TORCH_CHECK(t.numel() == 0 || reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, what,
+              " must start on a 16-byte boundary");
 }
 
 void check_i32(const Tensor& t, const char* what) {

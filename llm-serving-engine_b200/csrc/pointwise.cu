@@ -64,6 +64,42 @@ __device__ __forceinline__ void store4<bf16>(bf16* p, const float (&v)[4]) {
   *reinterpret_cast<uint2*>(p) = t;
 }
 
+// V = 4 or 8 elements at a time (8: two groups of four for float, one 16-byte vector for bfloat16)
+template <typename T, int V>
+__device__ __forceinline__ void loadv(const T* p, float (&v)[V]) {
+  if constexpr (V == 4) {
+    load4<T>(p, v);
+  } else if constexpr (std::is_same<T, bf16>::value) {
+    const Vec16<bf16> t = load16(p);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(t.v[j]);
+  } else {
+    float lo[4], hi[4];
+    load4<T>(p, lo);
+    load4<T>(p + 4, hi);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = lo[j];
+      v[j + 4] = hi[j];
+    }
+  }
+}
+template <typename T, int V>
+__device__ __forceinline__ void storev(T* p, const float (&v)[V]) {
+  if constexpr (V == 4) {
+    store4<T>(p, v);
+  } else if constexpr (std::is_same<T, bf16>::value) {
+    Vec16<bf16> t;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t.v[j] = __float2bfloat16_rn(v[j]);
+    store16(p, t);
+  } else {
+    const float lo[4] = {v[0], v[1], v[2], v[3]}, hi[4] = {v[4], v[5], v[6], v[7]};
+    store4<T>(p, lo);
+    store4<T>(p + 4, hi);
+  }
+}
+
 // VEC4: H is a multiple of 4, so rows are read and written four elements at a time.
 template <typename TR, typename TO, bool VEC4>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TR* __restrict__ residual,
@@ -123,6 +159,63 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TR* __restrict__
       float v = xr[i];
       if (rr && !in_place) v += Num<TR>::to_float(rr[i]);
       o[i] = Num<TO>::from_float(v * inv * weight[i]);
+    }
+  }
+}
+
+// The same for rows that fit the block's registers (H a multiple of 4, at most blockDim * 4 * NV):
+// each thread keeps its NV groups of four elements between the two visits, so a row is read from
+// memory once and every load of a row is in flight together.
+template <typename TR, typename TO, int NV>
+__global__ void add_rmsnorm_regs_kernel(float* __restrict__ x, const TR* __restrict__ residual,
+                                        const float* __restrict__ weight, float eps,
+                                        TO* __restrict__ out, const int* __restrict__ rows, int H) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  float w[NV][4];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {  // the weights are no result of the kernel before this one
+    const int i = (k * blockDim.x + threadIdx.x) * 4;
+    if (i < H) load4<float>(weight + i, w[k]);
+  }
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src_row = rows ? rows[r] : r;
+  float* xr = x + (size_t)src_row * H;
+  const TR* rr = residual ? residual + (size_t)src_row * H : nullptr;
+  const bool in_place = (rows == nullptr) && (rr != nullptr);
+  TO* o = out + (size_t)r * H;
+  float v[NV][4];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (k * blockDim.x + threadIdx.x) * 4;
+    if (i < H) load4<float>(xr + i, v[k]);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (k * blockDim.x + threadIdx.x) * 4;
+    if (i < H) {
+      if (rr) {
+        float a[4];
+        load4<TR>(rr + i, a);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[k][j] += a[j];
+        if (in_place) store4<float>(xr + i, v[k]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += v[k][j] * v[k][j];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = (k * blockDim.x + threadIdx.x) * 4;
+    if (i < H) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[k][j] = v[k][j] * inv * w[k][j];
+      store4<TO>(o + i, v[k]);
     }
   }
 }
@@ -196,7 +289,9 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
                                          T* __restrict__ v_pages,
                                          const int* __restrict__ block_tables, int table_stride,
                                          int page_tokens, int page_shift, int zero_in) {
-  constexpr int V = 4;  // elements per item and half
+  // elements per item and half: a 16-byte vector when both sides are bfloat16 (D is a multiple of
+  // 16 there, so a half holds whole vectors), four otherwise
+  constexpr int V = (std::is_same<TIn, bf16>::value && std::is_same<T, bf16>::value) ? 8 : 4;
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -218,18 +313,18 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
   for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < n_items; it += gridDim.y * blockDim.x) {
     const int head = it / chunks, i = (it - head * chunks) * V;
     const TIn* h = row + (size_t)head * D;
-    float a[4], b[4];
-    load4<TIn>(h + i, a);
-    load4<TIn>(h + i + half, b);
+    float a[V], b[V];
+    loadv<TIn, V>(h + i, a);
+    loadv<TIn, V>(h + i + half, b);
     if (!std::is_same<TIn, T>::value && zero_in) {
-      const float z[4] = {0.f, 0.f, 0.f, 0.f};
-      store4<TIn>(const_cast<TIn*>(h) + i, z);
-      store4<TIn>(const_cast<TIn*>(h) + i + half, z);
+      const float z[V] = {};
+      storev<TIn, V>(const_cast<TIn*>(h) + i, z);
+      storev<TIn, V>(const_cast<TIn*>(h) + i + half, z);
     }
     if (head < nq + nk && c) {
-      float cv[4], sv[4];
-      load4<float>(c + i, cv);
-      load4<float>(s + i, sv);
+      float cv[V], sv[V];
+      loadv<float, V>(c + i, cv);
+      loadv<float, V>(s + i, sv);
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         const float x1 = a[e], x2 = b[e];
@@ -239,19 +334,27 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
     }
     if (head < nq) {
       T* dst = qrow + (size_t)head * D;
-      store4<T>(dst + i, a);
-      store4<T>(dst + i + half, b);
+      storev<T, V>(dst + i, a);
+      storev<T, V>(dst + i + half, b);
     } else if (k_pages) {
       const bool is_k = head < nq + nk;
       const int kvh = is_k ? head - nq : head - nq - nk;
       T* dst = (is_k ? k_pages : v_pages) + page_base + (size_t)kvh * page_tokens * D;
-      store4<T>(dst + i, a);
-      store4<T>(dst + i + half, b);
+      storev<T, V>(dst + i, a);
+      storev<T, V>(dst + i + half, b);
     }
   }
 }
 
 // ------------------------------------------------------------------------------------ silu * up
+// silu(a) * u. A bfloat16 result keeps 8 bits of mantissa, so the fast exponential and division
+// (relative error near 1e-6) give the same stored value as the exact ones; float32 results use
+// the exact ones.
+template <typename T>
+__device__ __forceinline__ float silu_times(float a, float u) {
+  if constexpr (std::is_same<T, bf16>::value) return __fdividef(a, 1.f + __expf(-a)) * u;
+  else return a / (1.f + expf(-a)) * u;
+}
 template <typename TIn, typename T>
 __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I, int zero_in) {
   pdl_trigger();
@@ -271,13 +374,50 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out,
         store4<TIn>(const_cast<TIn*>(u) + i, z);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) gv[j] = gv[j] / (1.f + expf(-gv[j])) * uv[j];
+      for (int j = 0; j < 4; ++j) gv[j] = silu_times<T>(gv[j], uv[j]);
       store4<T>(o + i, gv);
     }
   } else {
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < I; i += gridDim.y * blockDim.x) {
-      const float a = Num<TIn>::to_float(g[i]);
-      o[i] = Num<T>::from_float(a / (1.f + expf(-a)) * Num<TIn>::to_float(u[i]));
+      o[i] = Num<T>::from_float(silu_times<T>(Num<TIn>::to_float(g[i]), Num<TIn>::to_float(u[i])));
+    }
+  }
+}
+
+// The same for input and output of one type and I a multiple of a 16-byte vector: the [T, I]
+// outputs are one flat list of vectors, two per thread a whole grid apart.
+template <typename T>
+__global__ void silu_mul_wide_kernel(const T* __restrict__ gu, T* __restrict__ out, int I,
+                                     unsigned total) {
+  constexpr int V = Num<T>::kVec;
+  pdl_trigger();
+  pdl_wait();
+  const unsigned per_row = (unsigned)I / V;
+  const unsigned stride = gridDim.x * blockDim.x;
+  const unsigned first = blockIdx.x * blockDim.x + threadIdx.x;
+  Vec16<T> g[2], u[2];
+  unsigned t[2], c[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const unsigned idx = first + k * stride;
+    if (idx < total) {
+      t[k] = idx / per_row;
+      c[k] = idx - t[k] * per_row;
+      const T* gp = gu + (size_t)t[k] * 2 * I + (size_t)c[k] * V;
+      g[k] = load16(gp);
+      u[k] = load16(gp + I);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const unsigned idx = first + k * stride;
+    if (idx < total) {
+      Vec16<T> o;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        o.v[j] = Num<T>::from_float(silu_times<T>(Num<T>::to_float(g[k].v[j]), Num<T>::to_float(u[k].v[j])));
+      }
+      store16(out + (size_t)t[k] * I + (size_t)c[k] * V, o);
     }
   }
 }
@@ -312,10 +452,16 @@ extern "C" int lse_add_rmsnorm(float* x, const void* residual, int residual_dtyp
                                const float* weight, float eps, void* out, int out_dtype,
                                const int* rows, int T, int H, cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+  // Rows of up to 16384 elements: 16 elements per thread, held in registers, so that many rows
+  // are resident on an SM together. Longer rows: the kernel that visits the row twice.
+  const bool regs = H % 4 == 0 && H <= 16384;
+  const int threads = regs ? ((H + 15) / 16 + 31) / 32 * 32 : 1024;
 #define LSE_NORM(TR, TO)                                                      \
   do {                                                                        \
-    if (H % 4 == 0)                                                           \
+    if (regs)                                                                 \
+      launch(add_rmsnorm_regs_kernel<TR, TO, 4>, T, threads, 0, stream,       \
+             x, (const TR*)residual, weight, eps, (TO*)out, rows, H);         \
+    else if (H % 4 == 0)                                                      \
       launch(add_rmsnorm_kernel<TR, TO, true>, T, threads, 0, stream,         \
              x, (const TR*)residual, weight, eps, (TO*)out, rows, H);         \
     else                                                                      \
@@ -344,13 +490,14 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
   if (in_dtype != dtype && in_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
   if (in_dtype == dtype && q_out != qkv) return LSE_BAD_ARGUMENT;  // same type: rotated in place
   const int ps = shift_of(page_tokens);
-  const bool vec = (D / 2) % 4 == 0;
+  const bool wide = in_dtype == LSE_BF16 && dtype == LSE_BF16 && (D / 2) % 8 == 0;  // the kernel's V = 8
+  const bool vec = (D / 2) % 4 == 0 && (wide || !(in_dtype == LSE_BF16 && dtype == LSE_BF16));
 #define LSE_ROPE_VEC(TIn, T)                                                                      \
   launch(rope_kv_write_vec_kernel<TIn, T>, vgrid, 128, 0, stream,                                 \
          (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,      \
          (T*)v_pages, block_tables, table_stride, page_tokens, ps, zero_in)
-  // one thread per item (head, chunk of 4 + 4 elements): every load of a token is in flight at once
-  const int items = (nq + 2 * nk) * (D / 8);
+  // one thread per item (head, chunk of V + V elements): every load of a token is in flight at once
+  const int items = (nq + 2 * nk) * (D / (wide ? 16 : 8));
   const dim3 vgrid(T, (items + 127) / 128 > 64 ? 64 : (items + 127) / 128);
   if (vec && in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ROPE_VEC(float, float);
   else if (vec && in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ROPE_VEC(bf16, bf16);
@@ -375,6 +522,17 @@ extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, 
   if (T <= 0 || I <= 0) return LSE_OK;
   if (zero_in && !(in_dtype == LSE_F32 && dtype == LSE_BF16 && I % 4 == 0)) return LSE_BAD_ARGUMENT;
   const int threads = 256;
+  const int vec = in_dtype == LSE_BF16 ? 8 : 4;
+  if (in_dtype == dtype && I % vec == 0 && (size_t)T * (I / vec) < (1ull << 31) &&
+      (reinterpret_cast<uintptr_t>(gu) % 16) == 0 && (reinterpret_cast<uintptr_t>(out) % 16) == 0) {
+    const unsigned total = (unsigned)((size_t)T * (I / vec));
+    const unsigned blocks = (total + 2 * threads - 1) / (2 * threads);
+    if (dtype == LSE_F32)
+      launch(silu_mul_wide_kernel<float>, blocks, threads, 0, stream, (const float*)gu, (float*)out, I, total);
+    else
+      launch(silu_mul_wide_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gu, (bf16*)out, I, total);
+    return LSE_CHECK_LAUNCH();
+  }
   const int per_block = threads * 4;
   dim3 grid(T, min((I + per_block - 1) / per_block, 65535));
   if (in_dtype == LSE_F32 && dtype == LSE_F32)

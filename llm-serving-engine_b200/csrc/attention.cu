@@ -397,6 +397,61 @@ struct DecodeShape {
 
 constexpr int DEC_WARPS = 4;
 
+constexpr int MERGE_SPLITS = 64;  // most context partitions per (sequence, head)
+
+// Merge of the partitions of one (sequence, head group), by the block that finished last. All its
+// loads are independent of one another: a warp per head fetches every partition's maximum and sum
+// at once and turns them into weights; then a thread per (head, dim) fetches the partitions'
+// values eight at a time. Kept out of line so that it does not disturb the register allocation
+// and instruction order of the key loop.
+template <typename T, int GT>
+__device__ __noinline__ void merge_partitions(const float* __restrict__ parts, int num_splits,
+                                              int heads_here, T* __restrict__ out) {
+  // parts: partition 0 of this block's first head; heads are num_splits * (D + 2) floats apart.
+  // out: this token's row at the first head.
+  __shared__ float sm_w[GT][MERGE_SPLITS], sm_L[GT];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int gq = warp; gq < heads_here; gq += DEC_WARPS) {
+    const float* part = parts + (size_t)gq * num_splits * (D + 2);
+    float ms[MERGE_SPLITS / 32], ls[MERGE_SPLITS / 32];
+#pragma unroll
+    for (int k = 0; k < MERGE_SPLITS / 32; ++k) {
+      const int sp = lane + 32 * k;
+      ms[k] = sp < num_splits ? __ldcg(part + sp * (D + 2) + D) : -INFINITY;
+      ls[k] = sp < num_splits ? __ldcg(part + sp * (D + 2) + D + 1) : 0.f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < MERGE_SPLITS / 32; ++k) M = fmaxf(M, ms[k]);
+    M = warp_max(M);
+    float L = 0.f;
+#pragma unroll
+    for (int k = 0; k < MERGE_SPLITS / 32; ++k) {
+      const float wt = (ms[k] == -INFINITY) ? 0.f : Exp<T>::f(ms[k] - M);
+      sm_w[gq][lane + 32 * k] = wt;
+      L += ls[k] * wt;
+    }
+    L = warp_sum(L);
+    if (lane == 0) sm_L[gq] = L;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < heads_here * D; idx += blockDim.x) {
+    const int gq = idx / D, d = idx - gq * D;
+    const float* part = parts + (size_t)gq * num_splits * (D + 2) + d;
+    float A = 0.f;
+#pragma unroll 1
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s0 + u < num_splits ? __ldcg(part + (s0 + u) * (D + 2)) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) A += v[u] * sm_w[gq][min(s0 + u, MERGE_SPLITS - 1)];
+    }
+    const float L = sm_L[gq];
+    out[idx] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+  }
+}
+
 template <typename T, int GT>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_split_kernel(const LseAttnArgs a, int page_shift) {
@@ -584,23 +639,9 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < heads_here * D; idx += blockDim.x) {
-    const int gq = idx / D, d = idx - gq * D;
-    const int h = h0 + gq;
-    const float* part =
-        a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h) * a.num_splits * (D + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < a.num_splits; ++s) M = fmaxf(M, __ldcg(part + s * (D + 2) + D));
-    float L = 0.f, A = 0.f;
-    for (int s = 0; s < a.num_splits; ++s) {
-      const float ms = __ldcg(part + s * (D + 2) + D);
-      const float wt = (ms == -INFINITY) ? 0.f : Exp<T>::f(ms - M);
-      L += __ldcg(part + s * (D + 2) + D + 1) * wt;
-      A += __ldcg(part + s * (D + 2) + d) * wt;
-    }
-    T* o = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
-    o[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
-  }
+  merge_partitions<T, GT>(
+      a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
+      a.num_splits, heads_here, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
 }
 
 static int shift_of(int n) {
@@ -625,6 +666,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   dim3 grid(a->num_splits, a->num_kv_heads * ((G + gt - 1) / gt), a->num_decode);
   if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
   if (a->num_splits > 1 && (size_t)grid.y * grid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
+  if (a->num_splits > MERGE_SPLITS) return LSE_BAD_ARGUMENT;
   if (gt == 1) launch(decode_split_kernel<T, 1>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   else if (gt == 2) launch(decode_split_kernel<T, 2>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   else launch(decode_split_kernel<T, 4>, grid, DEC_WARPS * 32, 0, stream, *a, ps);

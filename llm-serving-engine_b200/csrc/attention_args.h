@@ -32,7 +32,7 @@ struct LseAttnArgs {
   // single tokens
   const int* decode_seqs;  // [num_decode] sequence indices with one row each
   int num_decode;
-  int num_splits;          // context partitions per (sequence, head)
+  int num_splits;          // context partitions per (sequence, head): 1 to 64
   float* scratch;          // if num_splits > 1: lse_attn_decode_scratch_floats(...) floats; its
                            // first LSE_ATTN_COUNTERS words are counters that must be zero before
                            // a launch (every launch leaves them zero)

@@ -235,7 +235,7 @@ def test_attention_window_edges(ops, dtype, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("splits", [1, 3, 16])
+@pytest.mark.parametrize("splits", [1, 3, 16, 40, 64])
 def test_decode_split_counts_agree(ops, dtype, splits):
     q_lens, ctx_lens = [1, 1, 1], [1000, 17, 255]
     case = paged_case(3, q_lens, ctx_lens, 6, 2, 64, 16, DT[dtype], seed=8)

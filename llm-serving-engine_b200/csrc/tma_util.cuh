@@ -9,7 +9,8 @@
 namespace lse {
 namespace tma {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
+// polls of a barrier before a wait gives up: about half a second, against waits of microseconds
+constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);

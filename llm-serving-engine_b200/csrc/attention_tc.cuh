@@ -185,34 +185,55 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   pdl_wait();  // queries, keys and values were written by the kernel before this one
 
   if (warp == SOFTMAX_WARPS) {
+    // ---- TMA producer. The whole warp looks up block-table entries, one box of a key/value tile
+    // per lane and 32 boxes at a time, so that the lookups of several tiles are one round trip
+    // to memory; lane 0 then waits for free stages and issues the copies, with the rows handed
+    // over by shuffles. The other lanes rest at the warp barrier meanwhile.
     if (lane == 0) {
-      // ---- TMA producer
       mbar_expect_tx(q_full, Q_BYTES);
       tma_load_2d(q_tile, &map_q, q_full, head * HD, q_start + q0);
-      const int* table = a.block_tables + (size_t)seq * a.table_stride;
-      const int last_page_idx = (k_end - 1) >> p.page_shift;
-      const int boxes = KT / p.box_rows;
-      for (int it = 0; it < n_tiles && !failed; ++it) {
-        const int s = it % STAGES;
-        if (it >= STAGES && !mbar_wait(&kv_empty[s], ((it / STAGES) - 1) & 1)) {
-          failed = 1;
-          break;
+    }
+    const int* table = a.block_tables + (size_t)seq * a.table_stride;
+    const int last_page_idx = (k_end - 1) >> p.page_shift;
+    const int boxes = KT / p.box_rows;  // 1, 2, 4 or 8
+    const int group = 32 / boxes;       // tiles looked up together
+    int ok = 1;
+    for (int g0 = 0; g0 < n_tiles && ok; g0 += group) {
+      const int t_l = g0 + lane / boxes, b_l = lane % boxes;
+      int row_l = 0;
+      if (t_l < n_tiles) {
+        const int j = t_l * KT + b_l * p.box_rows;
+        // a box past the context re-reads the last valid page: its keys are masked anyway,
+        // and what it brings is finite
+        const int pi = min(j >> p.page_shift, last_page_idx);
+        const int off = (j >> p.page_shift) <= last_page_idx ? (j & (a.page_tokens - 1)) : 0;
+        row_l = (table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off;
+      }
+      const int g_end = min(g0 + group, n_tiles);
+      for (int t = g0; t < g_end && ok; ++t) {
+        int rows[8];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) rows[b] = __shfl_sync(0xffffffffu, row_l, ((t - g0) * boxes + b) & 31);
+        if (lane == 0) {
+          const int s = t % STAGES;
+          if (failed || (t >= STAGES && !mbar_wait(&kv_empty[s], ((t / STAGES) - 1) & 1))) {
+            failed = 1;
+            ok = 0;
+          } else {
+            mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+              if (b < boxes) {
+                tma_load_2d(k_tiles + s * KV_BYTES + b * p.box_rows * HD * 2, &map_k, &kv_full[s], 0, rows[b]);
+                tma_load_2d(v_tiles + s * KV_BYTES + b * p.box_rows * HD * 2, &map_v, &kv_full[s], 0, rows[b]);
+              }
+            }
+            issued = t + 1;
+          }
         }
-        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
-        for (int b = 0; b < boxes; ++b) {
-          const int j = it * KT + b * p.box_rows;
-          // a box past the context re-reads the last valid page: its keys are masked anyway,
-          // and what it brings is finite
-          const int pi = min(j >> p.page_shift, last_page_idx);
-          const int off = (j >> p.page_shift) <= last_page_idx ? (j & (a.page_tokens - 1)) : 0;
-          const int row = (table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off;
-          tma_load_2d(k_tiles + s * KV_BYTES + b * p.box_rows * HD * 2, &map_k, &kv_full[s], 0, row);
-          tma_load_2d(v_tiles + s * KV_BYTES + b * p.box_rows * HD * 2, &map_v, &kv_full[s], 0, row);
-        }
-        issued = it + 1;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
       }
     }
-    __syncwarp();
   } else if (warp == SOFTMAX_WARPS + 1) {
     if (lane == 0) {
       // ---- MMA issuer

@@ -531,31 +531,43 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
         }
       }
     }
+    // The U keys of a lane group share one update of the running maximum: one rescaling of the
+    // sums for U keys instead of one per key.
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int gq = 0; gq < GT; ++gq) {
+      float d[U];
+      float m_new = m[gq];
 #pragma unroll
-      for (int gq = 0; gq < GT; ++gq) {
-        float d = 0.f;
+      for (int u = 0; u < U; ++u) {
+        d[u] = 0.f;
 #pragma unroll
         for (int c = 0; c < CPL; ++c)
 #pragma unroll
           for (int e = 0; e < VEC; ++e)
-            d = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[u][c].v[e]), d);
+            d[u] = fmaf(qreg[gq][c][e], Num<T>::to_float(kv[u][c].v[e]), d[u]);
 #pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        if (ok[u]) {  // uniform over the LPK lanes of a key
-          const float m_new = fmaxf(m[gq], d);
-          const float corr = Exp<T>::f(m[gq] - m_new);
-          const float p = Exp<T>::f(d - m_new);
-          l[gq] = l[gq] * corr + p;
-#pragma unroll
-          for (int c = 0; c < CPL; ++c)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e)
-              acc[gq][c][e] = fmaf(p, Num<T>::to_float(vv[u][c].v[e]), acc[gq][c][e] * corr);
-          m[gq] = m_new;
-        }
+        for (int o = LPK / 2; o > 0; o >>= 1) d[u] += __shfl_xor_sync(0xffffffffu, d[u], o);
+        if (ok[u]) m_new = fmaxf(m_new, d[u]);  // ok is uniform over the LPK lanes of a key
       }
+      const float m_fin = (m_new == -INFINITY) ? 0.f : m_new;  // no key yet: everything stays 0
+      const float corr = Exp<T>::f(m[gq] - m_fin);
+      float p[U], psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        p[u] = ok[u] ? Exp<T>::f(d[u] - m_fin) : 0.f;
+        psum += p[u];
+      }
+      l[gq] = l[gq] * corr + psum;
+#pragma unroll
+      for (int c = 0; c < CPL; ++c)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          float t = acc[gq][c][e] * corr;
+#pragma unroll
+          for (int u = 0; u < U; ++u) t = fmaf(p[u], Num<T>::to_float(vv[u][c].v[e]), t);
+          acc[gq][c][e] = t;
+        }
+      m[gq] = m_new;
     }
   }
 

@@ -212,12 +212,13 @@ class CudaOps:
         }
 
     def decode_splits(self, num_decode, num_kv_heads, max_ctx):
-        """Context partitions per (sequence, head): about six blocks per SM, 64 keys or more each."""
+        """Context partitions per (sequence, head): about six blocks per SM, 128 keys or more each
+        (measured at one sequence of 2176 keys: 8 partitions 13.3 µs, 16 10.9, 28 11.9, 34 12.1)."""
         if num_decode == 0:
             return 1
         blocks = num_decode * num_kv_heads
         want = max(1, (6 * self.num_sms + blocks - 1) // blocks)
-        return int(max(1, min(want, (max_ctx + 63) // 64, 64)))
+        return int(max(1, min(want, (max_ctx + 127) // 128, 64)))
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan):

@@ -25,7 +25,10 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     for (int i = threadIdx.x * V; i < H; i += blockDim.x * V) {
       Vec16<T> v = load16(src + i);
 #pragma unroll
-      for (int j = 0; j < V; ++j) dst[i + j] = Num<T>::to_float(v.v[j]);
+      for (int j = 0; j < V; j += 4)  // H % V == 0 and 16-byte aligned rows: whole float4 stores
+        *reinterpret_cast<float4*>(dst + i + j) =
+            make_float4(Num<T>::to_float(v.v[j]), Num<T>::to_float(v.v[j + 1]),
+                        Num<T>::to_float(v.v[j + 2]), Num<T>::to_float(v.v[j + 3]));
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = Num<T>::to_float(src[i]);

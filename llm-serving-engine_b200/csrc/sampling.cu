@@ -82,12 +82,23 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   if (temp < 1e-5f) {
     ArgMax a = {-INFINITY, 0x7fffffff};
     if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
-      for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
-        const float4 v = *reinterpret_cast<const float4*>(row + i);
-        a = better(a, ArgMax{v.x, i});
-        a = better(a, ArgMax{v.y, i + 1});
-        a = better(a, ArgMax{v.z, i + 2});
-        a = better(a, ArgMax{v.w, i + 3});
+      // four loads of a thread in flight at once: the row is read once and nothing else hides
+      // the latency of memory
+      const int step = blockDim.x * 4;
+      for (int i0 = threadIdx.x * 4; i0 < V; i0 += 4 * step) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          v[u] = i0 + u * step < V ? *reinterpret_cast<const float4*>(row + i0 + u * step)
+                                   : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i0 + u * step;
+          a = better(a, ArgMax{v[u].x, i});
+          a = better(a, ArgMax{v[u].y, i + 1});
+          a = better(a, ArgMax{v[u].z, i + 2});
+          a = better(a, ArgMax{v[u].w, i + 3});
+        }
       }
     } else {
       for (int i = threadIdx.x; i < V; i += blockDim.x) a = better(a, ArgMax{row[i], i});

@@ -67,13 +67,137 @@ __device__ float block_max(float v, float* scratch) {
   return warp_max(lane < nw ? scratch[lane] : -INFINITY);
 }
 
+// ---- the cut of top-k / top-p --------------------------------------------------------------
+// With z = logit / temperature and e = exp(z - max z), element i is kept iff fewer than k elements
+// lie strictly above it and their mass (sum of e) is below top_p * (sum of all e). The cut is the
+// smallest kept value. It is found without sorting and without a pass per bit:
+//   1. one pass puts every element into one of HIST_BINS bins of equal width over
+//      [max - HIST_RANGE, max] (count and mass per bin; everything below falls into the last bin)
+//      and a scan from the top finds the bin that holds the cut;
+//   2. if that bin holds few elements (it usually does) they are listed and ranked against each
+//      other: the cut is the smallest of them that is kept. Otherwise
+//   3. the same scan inside that bin (HIST_BINS sub-bins), then the elements of the sub-bin are
+//      listed and the cut is bisected among their values.
+// Masses are summed as 64-bit fixed point (40 fractional bits) with integer atomics, so the result
+// does not depend on the order of the additions: the same logits give the same cut on every run.
+constexpr int HIST_BINS = 2048;
+constexpr float HIST_RANGE = 32.f;
+constexpr int LIST_CAP = 2048;  // candidates that fit in the shared-memory list
+constexpr int KEPT_CAP = 4096;   // survivors of the cut that fit in the shared-memory list
+constexpr int SMALL_LIST = 256;  // up to this many candidates are ranked against each other
+
+__device__ __forceinline__ unsigned long long mass_fix(float z, float zmax) {
+  return (unsigned long long)(expf(z - zmax) * 1099511627776.f);  // 2^40; z <= zmax
+}
+__device__ __forceinline__ int bin1_of(float z, float zmax) {
+  const float t = (zmax - z) * ((float)HIST_BINS / HIST_RANGE);
+  return t >= (float)(HIST_BINS - 1) ? HIST_BINS - 1 : (int)t;  // also for z = -inf
+}
+__device__ __forceinline__ int bin2_of(float z, float zmax, int b1) {
+  const float t = ((zmax - z) * ((float)HIST_BINS / HIST_RANGE) - (float)b1) * (float)HIST_BINS;
+  return t <= 0.f ? 0 : (t >= (float)(HIST_BINS - 1) ? HIST_BINS - 1 : (int)t);
+}
+
+// Adds a 64-bit value to a 64-bit sum kept as two 32-bit words (low word first) with 32-bit
+// shared-memory atomics: the carry out of the low word is added to the high word. Integer sums do
+// not depend on the order of the additions.
+__device__ __forceinline__ void add_mass(unsigned long long* sum, unsigned long long x) {
+  unsigned int* w = reinterpret_cast<unsigned int*>(sum);
+  const unsigned int lo = (unsigned int)x, hi = (unsigned int)(x >> 32);
+  const unsigned int old = atomicAdd(&w[0], lo);
+  const unsigned int carry = (old + lo < old) ? 1u : 0u;
+  if (hi + carry) atomicAdd(&w[1], hi + carry);
+}
+
+template <typename V>
+__device__ __forceinline__ V warp_add(V v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Over the bins filled by the whole block: the lowest (largest index) non-empty bin whose top
+// element is still kept, given what lies above all bins (a_cnt, a_mass). Adds the content of the
+// bins above it to a_cnt / a_mass. Called by every thread; warp 0 works; result for all.
+__device__ int find_cut_bin(const int* cnt, const unsigned long long* mass, int count_limit,
+                            unsigned long long mass_limit, int& a_cnt, unsigned long long& a_mass,
+                            int* res) {
+  __syncthreads();  // the histogram is complete
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    constexpr int PER = HIST_BINS / 32;
+    int c = 0;
+    unsigned long long m = 0;
+#pragma unroll 16
+    for (int b = lane * PER; b < (lane + 1) * PER; ++b) {
+      c += cnt[b];
+      m += mass[b];
+    }
+    // what lies above this lane's bins
+    int pc = c;
+    unsigned long long pm = m;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int c2 = __shfl_up_sync(0xffffffffu, pc, o);
+      const unsigned long long m2 = __shfl_up_sync(0xffffffffu, pm, o);
+      if (lane >= o) {
+        pc += c2;
+        pm += m2;
+      }
+    }
+    int rc = a_cnt + pc - c;
+    unsigned long long rm = a_mass + pm - m;
+    int found = -1, fc = 0;
+    unsigned long long fm = 0;
+#pragma unroll 8
+    for (int b = lane * PER; b < (lane + 1) * PER; ++b) {
+      if (cnt[b] > 0 && rc < count_limit && rm < mass_limit) {
+        found = b;
+        fc = rc;
+        fm = rm;
+      }
+      rc += cnt[b];
+      rm += mass[b];
+    }
+    int best = found;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if (best < 0) {  // cannot happen (the maximum is always kept); keep the top bin
+      if (lane == 0) {
+        res[0] = 0;
+        res[1] = a_cnt;
+        *reinterpret_cast<unsigned long long*>(res + 2) = a_mass;
+      }
+    } else if (found == best) {
+      res[0] = best;
+      res[1] = fc;
+      *reinterpret_cast<unsigned long long*>(res + 2) = fm;
+    }
+  }
+  __syncthreads();
+  a_cnt = res[1];
+  a_mass = *reinterpret_cast<const unsigned long long*>(res + 2);
+  return res[0];
+}
+
+// CACHE: the scaled row is kept in shared memory after the first read (rows of up to about 50 000
+// elements); otherwise every pass reads it from global memory again.
+template <bool CACHE>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ min_p, const uint64_t* __restrict__ seed,
               const int* __restrict__ draw, int* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char sample_smem[];
+  // histogram (counts, masses), later the candidate list (keys, masses); then the cached row
+  int* h_cnt = reinterpret_cast<int*>(sample_smem);
+  unsigned long long* h_mass = reinterpret_cast<unsigned long long*>(sample_smem + HIST_BINS * 4);
+  float* zrow = reinterpret_cast<float*>(sample_smem + HIST_BINS * 12);
   __shared__ float fs[32];
   __shared__ ArgMax as[32];
+  __shared__ __align__(8) int res[4];
+  __shared__ int list_n;
+  __shared__ unsigned long long z_total;
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
@@ -108,37 +232,181 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     return;
   }
   const float inv_t = 1.f / temp;
+  auto Z = [&](int i) -> float { return CACHE ? zrow[i] : row[i] * inv_t; };
   float zmax = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) zmax = fmaxf(zmax, row[i] * inv_t);
-  zmax = block_max(zmax, fs);
+  {
+    const int step = blockDim.x;
+    for (int i0 = threadIdx.x; i0 < V; i0 += 4 * step) {
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = i0 + u * step < V ? row[i0 + u * step] * inv_t : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (CACHE && i0 + u * step < V) zrow[i0 + u * step] = v[u];
+        zmax = fmaxf(zmax, v[u]);
+      }
+    }
+  }
+  zmax = block_max(zmax, fs);  // its barriers also publish the cached row
   const int k = top_k[r];
   const float p = top_p[r], mp = min_p[r];
   uint32_t cut = 0;  // keep elements whose key is >= cut
   if ((k > 0 && k < V) || p < 1.f) {
-    float Z = 0.f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) Z += expf(row[i] * inv_t - zmax);
-    Z = block_sum(Z, fs);
-    const float mass_limit = p * Z;
     const int count_limit = (k > 0 && k < V) ? k : V + 1;
-    // smallest key u such that a value with key u would be kept:
-    //   (number of elements strictly above it) < k  and  (their mass) < top_p
-    uint32_t lo = 0, hi = float_key(zmax);  // the maximum is always kept
-    while (lo < hi) {
-      const uint32_t mid = lo + ((hi - lo) >> 1);
-      const float val = key_float(mid);
-      float mass = 0.f, cnt = 0.f;
+    // ---- level 1
+    for (int b = threadIdx.x; b < HIST_BINS; b += blockDim.x) {
+      h_cnt[b] = 0;
+      h_mass[b] = 0;
+    }
+    __syncthreads();
+    unsigned long long zsum = 0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float z = Z(i);
+      const unsigned long long e = mass_fix(z, zmax);
+      const int b = bin1_of(z, zmax);
+      atomicAdd(&h_cnt[b], 1);
+      if (e) add_mass(&h_mass[b], e);
+      zsum += e;
+    }
+    zsum = warp_add(zsum);
+    if (threadIdx.x == 0) z_total = 0;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) atomicAdd(&z_total, zsum);
+    __syncthreads();
+    unsigned long long mass_limit =
+        p < 1.f ? (unsigned long long)((double)fmaxf(p, 0.f) * (double)z_total) : ~0ull;
+    if (mass_limit == 0) mass_limit = 1;  // the maximum is always kept
+    int a_cnt = 0;
+    unsigned long long a_mass = 0;
+    const int b1 = find_cut_bin(h_cnt, h_mass, count_limit, mass_limit, a_cnt, a_mass, res);
+    // ---- few elements in bin b1 (the usual case): list them and rank them against each other
+    if (h_cnt[b1] <= SMALL_LIST) {
+      const int n = h_cnt[b1];
+      __syncthreads();  // everyone has read the count before the histogram becomes the list
+      uint32_t* s_key = reinterpret_cast<uint32_t*>(h_cnt);
+      unsigned long long* s_mass = h_mass;
+      if (threadIdx.x == 0) {
+        list_n = 0;
+        res[0] = (int)0xffffffffu;
+      }
+      __syncthreads();
       for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float z = row[i] * inv_t;
-        if (z > val) {
-          mass += expf(z - zmax);
-          cnt += 1.f;
+        const float z = Z(i);
+        if (bin1_of(z, zmax) == b1) {
+          const int at = atomicAdd(&list_n, 1);
+          s_key[at] = float_key(z);
+          s_mass[at] = mass_fix(z, zmax);
         }
       }
-      mass = block_sum(mass, fs);
-      cnt = block_sum(cnt, fs);
-      if (cnt < (float)count_limit && mass < mass_limit) hi = mid; else lo = mid + 1;
+      __syncthreads();
+      if (threadIdx.x < n) {
+        const uint32_t mine = s_key[threadIdx.x];
+        int c = a_cnt;
+        unsigned long long m = a_mass;
+        for (int j = 0; j < n; ++j)
+          if (s_key[j] > mine) {
+            c += 1;
+            m += s_mass[j];
+          }
+        if (c < count_limit && m < mass_limit) atomicMin(reinterpret_cast<unsigned int*>(&res[0]), mine);
+      }
+      __syncthreads();
+      cut = (uint32_t)res[0];
+    } else {
+    // ---- level 2: inside bin b1
+    for (int b = threadIdx.x; b < HIST_BINS; b += blockDim.x) {
+      h_cnt[b] = 0;
+      h_mass[b] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float z = Z(i);
+      if (bin1_of(z, zmax) == b1) {
+        const int b = bin2_of(z, zmax, b1);
+        atomicAdd(&h_cnt[b], 1);
+        const unsigned long long e = mass_fix(z, zmax);
+        if (e) add_mass(&h_mass[b], e);
+      }
+    }
+    const int b2 = find_cut_bin(h_cnt, h_mass, count_limit, mass_limit, a_cnt, a_mass, res);
+    // ---- level 3: the elements of sub-bin (b1, b2); the cut is one of their values
+    uint32_t* l_key = reinterpret_cast<uint32_t*>(h_cnt);
+    unsigned long long* l_mass = h_mass;
+    if (threadIdx.x == 0) list_n = 0;
+    __syncthreads();
+    uint32_t kmin = 0xffffffffu, kmax = 0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float z = Z(i);
+      if (bin1_of(z, zmax) == b1 && bin2_of(z, zmax, b1) == b2) {
+        const uint32_t key = float_key(z);
+        kmin = min(kmin, key);
+        kmax = max(kmax, key);
+        const int at = atomicAdd(&list_n, 1);
+        if (at < LIST_CAP) {
+          l_key[at] = key;
+          l_mass[at] = mass_fix(z, zmax);
+        }
+      }
+    }
+    // smallest and largest candidate key of the block (shared-memory atomics on two words)
+    if (threadIdx.x == 0) {
+      res[0] = (int)0xffffffffu;
+      res[1] = 0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+      kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+    }
+    if ((threadIdx.x & 31) == 0 && kmin <= kmax) {
+      atomicMin(reinterpret_cast<unsigned int*>(&res[0]), kmin);
+      atomicMax(reinterpret_cast<unsigned int*>(&res[1]), kmax);
+    }
+    __syncthreads();
+    kmin = (uint32_t)res[0];
+    kmax = (uint32_t)res[1];
+    __syncthreads();
+    const int n = list_n;
+    // smallest key u in [kmin, kmax] such that fewer than k elements and less than the mass limit
+    // lie strictly above u; kmax is kept (its sub-bin was chosen for that)
+    uint32_t lo = kmin, hi = kmax;
+    while (lo < hi) {
+      const uint32_t mid = lo + ((hi - lo) >> 1);
+      int c = 0;
+      unsigned long long m = 0;
+      if (n <= LIST_CAP) {
+        for (int j = threadIdx.x; j < n; j += blockDim.x)
+          if (l_key[j] > mid) {
+            c += 1;
+            m += l_mass[j];
+          }
+      } else {  // more equal-looking values than the list holds: scan the row
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+          const float z = Z(i);
+          if (bin1_of(z, zmax) == b1 && bin2_of(z, zmax, b1) == b2 && float_key(z) > mid) {
+            c += 1;
+            m += mass_fix(z, zmax);
+          }
+        }
+      }
+      c = warp_add(c);
+      m = warp_add(m);
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        res[0] = 0;
+        z_total = 0;
+      }
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0 && c) {
+        atomicAdd(&res[0], c);
+        atomicAdd(&z_total, m);
+      }
+      __syncthreads();
+      if (a_cnt + res[0] < count_limit && a_mass + z_total < mass_limit) hi = mid; else lo = mid + 1;
     }
     cut = lo;
+    }
   }
   const float min_z = mp > 0.f ? zmax + logf(mp) : -INFINITY;
   const uint64_t sd = seed[r];
@@ -146,18 +414,59 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const uint32_t dr = (uint32_t)draw[r];
   ArgMax best = {-INFINITY, 0x7fffffff};
   const int quads = (V + 3) >> 2;
-  for (int qd = threadIdx.x; qd < quads; qd += blockDim.x) {
-    uint32_t c[4] = {(uint32_t)qd, dr, 0u, 0u};
-    philox4x32_10(c, k0, k1);
+  // The draw adds -log(-log u) to z - zmax, with u a multiple of 2^-24 plus 2^-25 inside (0, 1):
+  // that term lies in [-2.86, 17.33]. An element more than 20.2 below the maximum therefore loses
+  // to the maximum whatever is drawn, and needs no random number.
+  const float floor_z = zmax - 20.5f;
+  auto kept = [&](float z) { return float_key(z) >= cut && z >= min_z && z >= floor_z; };
+  auto score = [&](int i, float z, uint32_t bits) {
+    const float u = ((float)(bits >> 8) + 0.5f) * (1.f / 16777216.f);  // (0, 1)
+    // argmax of p_i / E_i with E_i = -log(u): compare log p_i - log E_i
+    return ArgMax{z - zmax - logf(-logf(u)), i};
+  };
+  bool listed = false;
+  if (cut > 0 || mp > 0.f) {
+    // Few elements survive a cut. They are listed first, so that the random numbers (made per
+    // group of four vocabulary entries, whoever asks) are computed by as many threads as there
+    // are survivors instead of by every warp that holds one.
+    int* kept_idx = reinterpret_cast<int*>(h_mass);
+    __syncthreads();  // the histogram and the candidate list are no longer read
+    if (threadIdx.x == 0) list_n = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x)
+      if (kept(Z(i))) {
+        const int at = atomicAdd(&list_n, 1);
+        if (at < KEPT_CAP) kept_idx[at] = i;
+      }
+    __syncthreads();
+    const int n = list_n;
+    if (n <= KEPT_CAP) {
+      listed = true;
+      for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        const int i = kept_idx[j];
+        uint32_t c[4] = {(uint32_t)(i >> 2), dr, 0u, 0u};
+        philox4x32_10(c, k0, k1);
+        best = better(best, score(i, Z(i), c[i & 3]));
+      }
+    }
+  }
+  if (!listed) {
+    for (int qd = threadIdx.x; qd < quads; qd += blockDim.x) {
+      float z[4];
+      bool keep[4], any = false;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int i = qd * 4 + e;
-      if (i >= V) break;
-      const float z = row[i] * inv_t;
-      if (float_key(z) < cut || z < min_z) continue;
-      const float u = ((float)(c[e] >> 8) + 0.5f) * (1.f / 16777216.f);  // (0, 1)
-      // argmax of p_i / E_i with E_i = -log(u): compare log p_i - log E_i
-      best = better(best, ArgMax{z - zmax - logf(-logf(u)), i});
+      for (int e = 0; e < 4; ++e) {
+        const int i = qd * 4 + e;
+        z[e] = i < V ? Z(i) : -INFINITY;
+        keep[e] = i < V && kept(z[e]);
+        any |= keep[e];
+      }
+      if (!any) continue;
+      uint32_t c[4] = {(uint32_t)qd, dr, 0u, 0u};
+      philox4x32_10(c, k0, k1);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (keep[e]) best = better(best, score(qd * 4 + e, z[e], c[e]));
     }
   }
   best = block_argmax(best, as);
@@ -210,8 +519,25 @@ extern "C" int lse_sample(const float* logits, int R, int V, const float* temper
                           cudaStream_t stream) {
   if (R <= 0) return LSE_OK;
   if (V <= 0) return LSE_BAD_ARGUMENT;
-  launch(sample_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, top_k, top_p, min_p,
-         seed, draw, out_tokens);
+  // histogram / candidate list, and the row itself when it fits beside them
+  const size_t base = (size_t)HIST_BINS * 12;
+  const size_t cached = base + (size_t)V * 4;
+  static int max_smem = -1;
+  if (max_smem < 0) {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    max_smem = v;
+    if (cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             max_smem - 4096) != cudaSuccess)
+      return LSE_LAUNCH_FAILED;
+  }
+  if (cached <= (size_t)max_smem - 4096)
+    launch(sample_kernel<true>, R, SAMPLE_THREADS, cached, stream, logits, V, temperature, top_k, top_p,
+           min_p, seed, draw, out_tokens);
+  else
+    launch(sample_kernel<false>, R, SAMPLE_THREADS, base, stream, logits, V, temperature, top_k, top_p,
+           min_p, seed, draw, out_tokens);
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 

@@ -170,6 +170,52 @@ class PlainOps:
             out[r] = int(score.argmax())
         return out
 
+    def sample_sorted(self, logits, temperature, top_k, top_p, min_p, seed, draw):
+        """The same rule as :meth:`sample` with a sort instead of the all-pairs comparison, for
+        vocabularies too large for a V x V matrix. An element's strictly-above count and mass are
+        those of the first element of its group of equal values in descending order; masses are
+        summed in float64."""
+        R, V = logits.shape
+        out = torch.empty(R, dtype=torch.int32)
+        for r in range(R):
+            t = float(temperature[r])
+            row = logits[r].float()
+            if t < 1e-5:
+                out[r] = int(row.argmax())
+                continue
+            z = row * np.float32(1.0 / np.float32(t))
+            zmax = z.max()
+            p = torch.exp(z - zmax).double()
+            keep = torch.ones(V, dtype=torch.bool)
+            k, tp, mp = int(top_k[r]), float(top_p[r]), float(min_p[r])
+            if (0 < k < V) or tp < 1.0:
+                zs, order = torch.sort(z, descending=True, stable=True)
+                ps = p[order]
+                excl = torch.cumsum(ps, 0) - ps  # mass before each sorted position
+                first = torch.ones(V, dtype=torch.bool)
+                first[1:] = zs[1:] != zs[:-1]
+                start = torch.cummax(torch.where(first, torch.arange(V), torch.zeros(V, dtype=torch.long)), 0).values
+                count, mass = start, excl[start]
+                ks = torch.ones(V, dtype=torch.bool)
+                if 0 < k < V:
+                    ks &= count < k
+                ks &= mass < float(np.float32(tp)) * float(p.sum())
+                keep[order] = ks
+            if mp > 0:
+                keep &= z >= zmax + np.log(np.float32(mp))
+            sd = int(seed[r]) & 0xFFFFFFFFFFFFFFFF
+            quads = np.arange((V + 3) // 4, dtype=np.uint32)
+            c = philox4x32_10(
+                [quads, np.full_like(quads, int(draw[r])), np.zeros_like(quads), np.zeros_like(quads)],
+                sd & 0xFFFFFFFF, sd >> 32,
+            )
+            bits = np.stack(c, axis=1).reshape(-1)[:V].astype(np.uint32)
+            u = ((bits >> 8).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
+            score = (z - zmax) - torch.from_numpy(np.log(-np.log(u))).float()
+            score[~keep] = float("-inf")
+            out[r] = int(score.argmax())
+        return out
+
     def logsumexp(self, logits):
         return torch.logsumexp(logits.float(), dim=-1)
 

@@ -41,6 +41,24 @@ def test_matches_plain_sampler_draw_for_draw(ops, kw):
     assert got.tolist() == ref.tolist()
 
 
+@pytest.mark.parametrize("V", [49152, 70001])  # the row kept in shared memory, and too long for it
+@pytest.mark.parametrize("kw", [dict(top_k=50), dict(top_p=0.9), dict(top_p=0.999),
+                                dict(top_k=1000, top_p=0.95, min_p=0.001, temperature=0.6),
+                                dict(top_k=1), dict(top_p=1e-6)])
+def test_cut_on_a_large_vocabulary(ops, V, kw):
+    R = 5
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[1, ::7] = float("-inf")           # banned tokens
+    logits[2] = (logits[2] * 4).round() / 4  # many equal values: groups of ties across the cut
+    logits[3, :] = 0.25                      # all equal: everything is kept or only ties matter
+    p = params(R, seed=torch.arange(R) * 104729 + 11, draw=torch.arange(R) + 1, **kw)
+    for rep in range(2):  # the same launch twice: the cut does not depend on the order of additions
+        got = ops.sample(logits.cuda(), *[x.cuda() for x in p]).cpu()
+        ref = PlainOps().sample_sorted(logits, *p)
+        assert got.tolist() == ref.tolist()
+
+
 def test_draws_follow_the_distribution_and_the_cuts(ops):
     V, N = 5, 20000
     probs = torch.tensor([0.4, 0.3, 0.15, 0.1, 0.05])

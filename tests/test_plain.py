@@ -74,3 +74,22 @@ def test_forward_is_causal(tiny_dirs):
     full = plain_llama.model_logits(tiny_dirs["A"], ids)
     part = plain_llama.model_logits(tiny_dirs["A"], ids[:11])
     assert (full[:11] - part).abs().max() < 1e-5
+
+
+def test_the_two_plain_samplers_agree():
+    """The all-pairs rule and its sorted form keep the same elements and draw the same tokens."""
+    import torch
+
+    from plain_ops import PlainOps
+
+    R, V = 8, 611
+    g = torch.Generator().manual_seed(5)
+    logits = torch.randn(R, V, generator=g) * 2
+    logits[2] = (logits[2] * 2).round() / 2
+    logits[3, ::5] = float("-inf")
+    f = lambda v, dt: torch.full((R,), v, dtype=dt)
+    for k, tp, mp, t in [(0, 1.0, 0.0, 1.0), (7, 1.0, 0.0, 0.8), (0, 0.6, 0.0, 1.3), (40, 0.9, 0.05, 0.7),
+                         (1, 1.0, 0.0, 1.0), (0, 0.0, 0.0, 1.0)]:
+        args = (f(t, torch.float32), f(k, torch.int32), f(tp, torch.float32), f(mp, torch.float32),
+                torch.arange(R) * 31 + 1, torch.arange(R, dtype=torch.int32))
+        assert PlainOps().sample(logits, *args).tolist() == PlainOps().sample_sorted(logits, *args).tolist()

@@ -390,6 +390,41 @@ void apply_penalties(Tensor& logits, const Tensor& row, const Tensor& token, con
        "apply_penalties");
 }
 
+void token_state_add(Tensor& state, const Tensor& slot, const Tensor& token, const Tensor& in_prompt) {
+  check_i32(state, "state");
+  check_i32(slot, "slot");
+  check_i32(token, "token");
+  check_i32(in_prompt, "in_prompt");
+  TORCH_CHECK(state.dim() == 2, "token_state_add: state must be [slots, vocab]");
+  const int n = (int)slot.numel();
+  TORCH_CHECK(token.numel() == n && in_prompt.numel() == n, "token_state_add: lengths differ");
+  done(lse_token_state_add(state.data_ptr<int>(), (int)state.size(1), slot.data_ptr<int>(),
+                           token.data_ptr<int>(), in_prompt.data_ptr<int>(), n, stream()),
+       "token_state_add");
+}
+
+void apply_penalties_dense(Tensor& logits, const Tensor& row, const Tensor& slot, const Tensor& presence,
+                           const Tensor& frequency, const Tensor& repetition, const Tensor& state) {
+  check_f32(logits, "logits");
+  check_i32(row, "row");
+  check_i32(slot, "slot");
+  check_f32(presence, "presence");
+  check_f32(frequency, "frequency");
+  check_f32(repetition, "repetition");
+  check_i32(state, "state");
+  const int n = (int)row.numel();
+  TORCH_CHECK(slot.numel() == n && presence.numel() == n && frequency.numel() == n &&
+                  repetition.numel() == n,
+              "apply_penalties_dense: lengths differ");
+  TORCH_CHECK(logits.dim() == 2 && state.dim() == 2 && state.size(1) == logits.size(1),
+              "apply_penalties_dense: state must be [slots, vocab]");
+  done(lse_apply_penalties_dense(logits.data_ptr<float>(), (int)logits.size(1), row.data_ptr<int>(),
+                                 slot.data_ptr<int>(), presence.data_ptr<float>(),
+                                 frequency.data_ptr<float>(), repetition.data_ptr<float>(),
+                                 state.data_ptr<int>(), n, stream()),
+       "apply_penalties_dense");
+}
+
 void ban_tokens(Tensor& logits, const Tensor& row, const Tensor& token) {
   check_f32(logits, "logits");
   check_i32(row, "row");
@@ -420,4 +455,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("logsumexp", &logsumexp);
   m.def("apply_penalties", &apply_penalties);
   m.def("ban_tokens", &ban_tokens);
+  m.def("token_state_add", &token_state_add);
+  m.def("apply_penalties_dense", &apply_penalties_dense);
 }

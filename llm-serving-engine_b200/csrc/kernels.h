@@ -75,6 +75,16 @@ int lse_apply_penalties(float* logits, int V, const int* row, const int* token, 
                         int n, cudaStream_t stream);
 
 // logits[row[i], token[i]] = -inf
+// Token state of the penalties on the device: state[slots, V] int32, low 30 bits = times
+// generated, bit 30 = occurs in the prompt. lse_token_state_add enters n (slot, token) pairs
+// (in_prompt[i] != 0: mark as prompt token; else count one more generation).
+// lse_apply_penalties_dense applies presence / frequency / repetition (the rule above) to logits
+// row row[j] from the state of slot[j], for j < n.
+int lse_token_state_add(int* state, int V, const int* slot, const int* token, const int* in_prompt,
+                        int n, cudaStream_t stream);
+int lse_apply_penalties_dense(float* logits, int V, const int* row, const int* slot,
+                              const float* presence, const float* frequency, const float* repetition,
+                              const int* state, int n, cudaStream_t stream);
 int lse_ban_tokens(float* logits, int V, const int* row, const int* token, int n,
                    cudaStream_t stream);
 }

@@ -503,6 +503,42 @@ __global__ void penalties_kernel(float* __restrict__ logits, int V, const int* _
   *p = v;
 }
 
+// Per-request token state for the penalties, kept on the device: state[slot][v] counts how often
+// token v was generated (low 30 bits) and marks tokens of the prompt (bit 30). token_state_add
+// enters tokens; penalties_dense applies the rule of penalties_kernel to every marked entry of the
+// rows it is given, reading the state instead of a list built on the host.
+constexpr int PROMPT_BIT = 1 << 30;
+
+__global__ void token_state_add_kernel(int* __restrict__ state, int V, const int* __restrict__ slot,
+                                       const int* __restrict__ token,
+                                       const int* __restrict__ in_prompt, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int* p = state + (size_t)slot[i] * V + token[i];
+  if (in_prompt[i]) atomicOr(p, PROMPT_BIT);
+  else atomicAdd(p, 1);
+}
+
+__global__ void penalties_dense_kernel(float* __restrict__ logits, int V, const int* __restrict__ row,
+                                       const int* __restrict__ slot,
+                                       const float* __restrict__ presence,
+                                       const float* __restrict__ frequency,
+                                       const float* __restrict__ repetition,
+                                       const int* __restrict__ state) {
+  const int j = blockIdx.y;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= V) return;
+  const int st = state[(size_t)slot[j] * V + v];
+  if (st == 0) return;
+  float* p = logits + (size_t)row[j] * V + v;
+  float x = *p;
+  const int c = st & (PROMPT_BIT - 1);
+  if (c > 0) x -= frequency[j] * (float)c + presence[j];
+  const float rp = repetition[j];
+  if (rp != 1.f) x = x > 0.f ? x / rp : x * rp;
+  *p = x;
+}
+
 __global__ void ban_kernel(float* __restrict__ logits, int V, const int* __restrict__ row,
                            const int* __restrict__ token, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -560,5 +596,23 @@ extern "C" int lse_ban_tokens(float* logits, int V, const int* row, const int* t
                               cudaStream_t stream) {
   if (n <= 0) return LSE_OK;
   ban_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, V, row, token, n);
+  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+}
+
+extern "C" int lse_token_state_add(int* state, int V, const int* slot, const int* token,
+                                   const int* in_prompt, int n, cudaStream_t stream) {
+  if (n <= 0) return LSE_OK;
+  token_state_add_kernel<<<(n + 255) / 256, 256, 0, stream>>>(state, V, slot, token, in_prompt, n);
+  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+}
+
+extern "C" int lse_apply_penalties_dense(float* logits, int V, const int* row, const int* slot,
+                                         const float* presence, const float* frequency,
+                                         const float* repetition, const int* state, int n,
+                                         cudaStream_t stream) {
+  if (n <= 0 || V <= 0) return LSE_OK;
+  if (n > 65535) return LSE_BAD_ARGUMENT;
+  penalties_dense_kernel<<<dim3((V + 255) / 256, n), 256, 0, stream>>>(logits, V, row, slot, presence,
+                                                                       frequency, repetition, state);
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }

@@ -7,6 +7,10 @@ replayed: per step the host fills one pinned buffer (token ids, positions, conte
 tables, sampling parameters), copies it to the device in one transfer, replays the graph (model
 forward and sampling kernel) and reads the sampled token ids back.
 
+Rows that need more than the sampling kernel (penalties, banned tokens, log-probabilities) use a
+second capture of the same step that ends with the logits; the sampler then runs on them
+uncaptured. The model forward is replayed either way.
+
 The graph runs the same model code, kernels and cache as an uncaptured step; only the launch
 mechanism differs.
 """
@@ -22,9 +26,10 @@ from .batch import DeviceStep, StepEntry
 
 
 class _Graph:
-    def __init__(self, owner: "DecodeGraphs", batch: int, splits: int) -> None:
+    def __init__(self, owner: "DecodeGraphs", batch: int, splits: int, sampled: bool = True) -> None:
         runner = owner.runner
         self.batch = B = batch
+        self.sampled = sampled  # the capture ends with the sampling kernel (else with the logits)
         dev = runner.device
         widths = [-(-runner.max_model_len // g.page_tokens) for g in runner.manager.groups]
         # layout of the per-step buffer, in int32 words
@@ -67,6 +72,7 @@ class _Graph:
         self.h2d_done: torch.cuda.Event | None = None  # the pinned input buffer may be rewritten after it
         self.graph: torch.cuda.CUDAGraph | None = None
         self.tokens: torch.Tensor | None = None
+        self.logits: torch.Tensor | None = None
         self.launches = 0
 
     def hview(self, name, dtype=np.int32):
@@ -77,7 +83,7 @@ class _Graph:
 class DecodeGraphs:
     def __init__(self, runner) -> None:
         self.runner = runner
-        self.graphs: dict[tuple[int, int], _Graph] = {}
+        self.graphs: dict[tuple[int, int, bool], _Graph] = {}
         self.pool = None
         groups = runner.manager.groups
         self.min_kv_heads = min((g.num_kv_heads for g in groups), default=1)
@@ -90,16 +96,26 @@ class DecodeGraphs:
         self.mirror_epoch = np.zeros(runner.manager.max_requests, dtype=np.int64)
 
     @staticmethod
-    def usable(entries: Sequence[StepEntry], rows) -> bool:
+    def forward_usable(entries: Sequence[StepEntry], rows) -> bool:
+        """Every entry is one token whose logits are sampled."""
         if len(rows) != len(entries):
             return False
         for e in entries:
             if len(e.tokens) != 1 or list(e.want) != [0]:
                 return False
+        return True
+
+    @staticmethod
+    def simple(rows) -> bool:
+        """The sampling kernel alone serves these rows, so it is captured with the step."""
         for r in rows:
             if r.params.has_penalties or r.banned_token_ids or r.params.logprobs is not None:
                 return False
         return True
+
+    @staticmethod
+    def usable(entries: Sequence[StepEntry], rows) -> bool:
+        return DecodeGraphs.forward_usable(entries, rows) and DecodeGraphs.simple(rows)
 
     def _fill(self, g: _Graph, entries, rows, ahead: int = 0) -> int:
         """Write the step's inputs into the pinned buffer. ``ahead`` = 1 describes the step *after*
@@ -148,7 +164,7 @@ class DecodeGraphs:
     def _forward(self, g: _Graph):
         runner = self.runner
         logits = runner.model.forward(g.step, runner.pools)
-        return runner.ops.sample(logits, *g.sample_args)
+        return runner.ops.sample(logits, *g.sample_args) if g.sampled else logits
 
     def _capture(self, g: _Graph) -> None:
         ops = self.runner.ops
@@ -165,24 +181,34 @@ class DecodeGraphs:
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
         with torch.cuda.graph(g.graph, pool=self.pool):
-            g.tokens = self._forward(g)
+            out = self._forward(g)
+        if g.sampled:
+            g.tokens = out
+        else:
+            g.logits = out
         g.launches = ops.launches - before
 
-    def launch(self, entries: Sequence[StepEntry], rows, ahead_of: "Pending | None" = None) -> "Pending":
+    def launch(self, entries: Sequence[StepEntry], rows, ahead_of: "Pending | None" = None,
+               sampler=None) -> "Pending":
         """Enqueue a step (inputs copy, graph replay, token read-back) without waiting for it.
 
         With ``ahead_of`` the step continues the same sequences one position after that still
         running step and takes its input token ids on the device from that step's samples.
+        Rows that the sampling kernel alone cannot serve need ``sampler``: the replay then ends
+        with the logits and the sampler runs on them before this method returns.
         """
         runner = self.runner
         B = len(entries)
+        simple = self.simple(rows)
+        if not simple and (sampler is None or ahead_of is not None):
+            raise ValueError("these rows need a sampler and cannot run ahead")
         ahead = 0 if ahead_of is None else 1
         max_ctx = 1 + ahead + max(runner.manager.held[e.rid].computed for e in entries)
         splits = runner.ops.decode_splits(B, self.min_kv_heads, max_ctx)
-        key = (B, splits)
+        key = (B, splits, simple)
         g = self.graphs.get(key)
         if g is None:
-            g = self.graphs[key] = _Graph(self, B, splits)
+            g = self.graphs[key] = _Graph(self, B, splits, simple)
         if g.h2d_done is not None:
             g.h2d_done.synchronize()
         self._fill(g, entries, rows, ahead)
@@ -195,25 +221,32 @@ class DecodeGraphs:
             self._capture(g)
         g.graph.replay()
         runner.ops.launches += g.launches
+        runner.steps_run += 1
+        if not simple:
+            return Pending(g, None, None, sampler.sample(g.logits, rows))
         buf = g.tokens_host[g.turn]
         g.turn ^= 1
         buf.copy_(g.tokens, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        runner.steps_run += 1
         return Pending(g, done, buf)
 
     @staticmethod
-    def collect(pending: "Pending") -> list[int]:
-        pending.done.synchronize()
-        return pending.tokens_host.tolist()
+    def collect(pending: "Pending"):
+        """The step's :class:`~llmserve_b200.sampling.sampler.SamplerOutput` (waits for it)."""
+        from ..sampling.sampler import SamplerOutput
 
-    def run(self, entries: Sequence[StepEntry], rows) -> list[int]:
-        return self.collect(self.launch(entries, rows))
+        if pending.result is not None:
+            return pending.result
+        pending.done.synchronize()
+        return SamplerOutput(pending.tokens_host.tolist(), None, None)
+
+    def run(self, entries: Sequence[StepEntry], rows, sampler=None):
+        return self.collect(self.launch(entries, rows, sampler=sampler))
 
 
 class Pending:
-    """A launched step whose sampled tokens have not been read yet."""
+    """A launched step whose sampled tokens have not been read yet (``result``: already sampled)."""
 
-    def __init__(self, graph: _Graph, done, tokens_host) -> None:
-        self.graph, self.done, self.tokens_host = graph, done, tokens_host
+    def __init__(self, graph: _Graph, done, tokens_host, result=None) -> None:
+        self.graph, self.done, self.tokens_host, self.result = graph, done, tokens_host, result

@@ -118,7 +118,7 @@ class LLMEngine:
         )
         self.manager = self.runner.manager
         self.scheduler = Scheduler(cfg.scheduler_config(), self.manager)
-        self.sampler = Sampler(ops, cfg.device)
+        self.sampler = Sampler(ops, cfg.device, max_slots=self.manager.max_requests)
         self.detok = IncrementalDetokenizer(tokenizer) if tokenizer is not None else None
         self.requests: dict[str, Request] = {}
         self._seq_ids = itertools.count()
@@ -230,7 +230,7 @@ class LLMEngine:
         scheduled = [(s.seq, s.num_new_tokens) for s in sched.scheduled]
         flight = _InFlight(scheduled, sample_seqs, stats, t0)
         if self.cfg.cuda_graphs and self.runner.can_launch_decode(entries, rows):
-            flight.pending = self.runner.launch_decode(entries, rows)
+            flight.pending = self.runner.launch_decode(entries, rows, sampler=self.sampler)
         else:
             flight.result = self.runner.step_and_sample(entries, self.sampler, rows, graphs=False)
         return flight
@@ -238,6 +238,8 @@ class LLMEngine:
     def _launch_ahead(self, cur: "_InFlight"):
         """Launch the step after ``cur`` before ``cur``'s tokens are known, if the batch cannot change."""
         if cur.pending is None or not self.cfg.run_ahead or self.scheduler.waiting:
+            return None
+        if cur.pending.result is not None:  # sampled outside the graph: its tokens are on the host
             return None
         seqs = cur.sample_seqs
         if len(seqs) != len(cur.scheduled) or len(seqs) != len(self.scheduler.running):
@@ -252,7 +254,9 @@ class LLMEngine:
                 return None
         rows = [self._sample_row(seq, ahead=1) for seq in seqs]
         entries = [StepEntry(seq.seq_id, [0], [0]) for seq in seqs]
-        if not self.runner.can_launch_decode(entries, rows):
+        from .decode_graph import DecodeGraphs
+
+        if not (self.runner.can_launch_decode(entries, rows) and DecodeGraphs.simple(rows)):
             return None
         for seq in seqs:
             self.manager.allocate(seq.seq_id, 2)
@@ -265,11 +269,8 @@ class LLMEngine:
         """Read the step's tokens and do the host's part. Returns (outputs, batch unchanged)."""
         stats = cur.stats
         t1 = time.monotonic()
-        if cur.pending is not None:
-            tokens = self.runner.collect_decode(cur.pending)
-            logprobs = tops = None
-        else:
-            tokens, logprobs, tops = cur.result.token_ids, cur.result.logprobs, cur.result.top_logprobs
+        result = self.runner.collect_decode(cur.pending) if cur.pending is not None else cur.result
+        tokens, logprobs, tops = result.token_ids, result.logprobs, result.top_logprobs
         stats.t_forward = time.monotonic() - t1
         unchanged = True
         for seq, n in cur.scheduled:
@@ -313,8 +314,11 @@ class LLMEngine:
         banned = []
         if n_out < p.min_tokens:
             banned = sorted(self.eos_ids | set(p.stop_token_ids))
+        held = self.manager.held.get(seq.seq_id) if p.has_penalties else None
         return SampleRow(p, seq.output_token_ids, seq.prompt_token_ids, seq.seed, banned,
-                         draw=n_out if ahead else None)
+                         draw=n_out if ahead else None,
+                         slot=held.slot if held is not None else -1,
+                         epoch=held.epoch if held is not None else 0)
 
     def _append_token(self, seq, token, logprob, top, now) -> None:
         req = seq.request

@@ -195,21 +195,22 @@ class ModelRunner:
     def can_launch_decode(self, entries: Sequence[StepEntry], rows) -> bool:
         from .decode_graph import DecodeGraphs
 
-        return self.device.type == "cuda" and DecodeGraphs.usable(entries, rows)
+        return self.device.type == "cuda" and DecodeGraphs.forward_usable(entries, rows)
 
-    def launch_decode(self, entries: Sequence[StepEntry], rows, ahead_of=None):
-        """Enqueue a step of single tokens as a CUDA graph and return without waiting for it
-        (see :meth:`DecodeGraphs.launch`); :meth:`collect_decode` waits and returns the tokens."""
+    def launch_decode(self, entries: Sequence[StepEntry], rows, ahead_of=None, sampler=None):
+        """Enqueue a step of single tokens as a CUDA graph (see :meth:`DecodeGraphs.launch`);
+        :meth:`collect_decode` waits and returns the sampler's output. Rows with penalties, banned
+        tokens or log-probabilities need ``sampler`` and are sampled before this returns."""
         from .decode_graph import DecodeGraphs
 
         if self.decode_graphs is None:
             self.decode_graphs = DecodeGraphs(self)
-        pending = self.decode_graphs.launch(entries, rows, ahead_of)
+        pending = self.decode_graphs.launch(entries, rows, ahead_of, sampler)
         self.last_h2d_bytes = 4 * pending.graph.words
         self.last_d2h_bytes = 4 * len(entries)
         return pending
 
-    def collect_decode(self, pending) -> list[int]:
+    def collect_decode(self, pending):
         return self.decode_graphs.collect(pending)
 
     def step_and_sample(self, entries: Sequence[StepEntry], sampler, rows, graphs: bool = False):
@@ -217,18 +218,8 @@ class ModelRunner:
 
         ``rows`` has one :class:`~llmserve_b200.sampling.SampleRow` per wanted place, in order.
         """
-        if graphs and self.device.type == "cuda":
-            from ..sampling.sampler import SamplerOutput
-            from .decode_graph import DecodeGraphs
-
-            if DecodeGraphs.usable(entries, rows):
-                if self.decode_graphs is None:
-                    self.decode_graphs = DecodeGraphs(self)
-                tokens = self.decode_graphs.run(entries, rows)
-                g = self.decode_graphs
-                self.last_h2d_bytes = 4 * max(x.words for x in g.graphs.values() if x.batch == len(entries))
-                self.last_d2h_bytes = 4 * len(entries)
-                return SamplerOutput(tokens, None, None)
+        if graphs and self.can_launch_decode(entries, rows):
+            return self.collect_decode(self.launch_decode(entries, rows, sampler=sampler))
         logits = self.step(entries)
         out = sampler.sample(logits, rows)
         self.last_d2h_bytes = 4 * len(rows)

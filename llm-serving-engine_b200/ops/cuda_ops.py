@@ -262,6 +262,15 @@ class CudaOps:
         self.ext.ban_tokens(logits, row, token)
         self.launches += 1
 
+    def token_state_add(self, state, slot, token, in_prompt):
+        """Enter (slot, token) pairs into the penalties' token state ``[slots, vocab]`` (int32)."""
+        self.ext.token_state_add(state, slot, token, in_prompt)
+        self.launches += 1
+
+    def apply_penalties_dense(self, logits, row, slot, presence, frequency, repetition, state):
+        self.ext.apply_penalties_dense(logits, row, slot, presence, frequency, repetition, state)
+        self.launches += 1
+
 
 _instances: dict[str, CudaOps] = {}
 

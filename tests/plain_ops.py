@@ -230,5 +230,27 @@ class PlainOps:
                 v = v / rp if v > 0 else v * rp
             logits[r, t] = v
 
+    PROMPT_BIT = 1 << 30
+
+    def token_state_add(self, state, slot, token, in_prompt):
+        for s_, t, f in zip(slot.tolist(), token.tolist(), in_prompt.tolist()):
+            if f:
+                state[s_, t] |= self.PROMPT_BIT
+            else:
+                state[s_, t] += 1
+
+    def apply_penalties_dense(self, logits, row, slot, presence, frequency, repetition, state):
+        for j in range(row.shape[0]):
+            r, st = int(row[j]), state[int(slot[j])]
+            for t in torch.nonzero(st).flatten().tolist():
+                v = float(logits[r, t])
+                c = int(st[t]) & (self.PROMPT_BIT - 1)
+                if c > 0:
+                    v -= float(frequency[j]) * c + float(presence[j])
+                rp = float(repetition[j])
+                if rp != 1.0:
+                    v = v / rp if v > 0 else v * rp
+                logits[r, t] = v
+
     def ban_tokens(self, logits, row, token):
         logits[row.long(), token.long()] = float("-inf")

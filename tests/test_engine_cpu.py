@@ -135,3 +135,36 @@ def test_llm_generate_returns_outputs_in_input_order(sharp_dirs):
         assert o.outputs[0].token_ids == plain_llama.greedy(sharp_dirs["C"], p, 4)
     one = llm.generate(PROMPTS[3], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
     assert len(one) == 1 and len(one[0].outputs[0].token_ids) == 2
+
+
+def test_penalties_from_the_token_state_equal_penalties_from_host_lists():
+    """The sampler with state slots (tokens entered step by step into a [slots, vocab] state) and
+    the sampler without (penalised tokens listed on the host every step) change the logits in the
+    same way, also after a slot has passed to another request."""
+    import torch
+
+    from llmserve_b200.sampling.params import SamplingParams
+    from llmserve_b200.sampling.sampler import SampleRow, Sampler
+
+    V = 97
+    g = torch.Generator().manual_seed(3)
+    with_state = Sampler(PlainOps(), "cpu", max_slots=3)
+    without = Sampler(PlainOps(), "cpu")
+    pa = SamplingParams(temperature=0.0, repetition_penalty=1.7, presence_penalty=0.5, frequency_penalty=0.25)
+    pb = SamplingParams(temperature=0.0, frequency_penalty=1.5)
+    plain = SamplingParams(temperature=0.0)
+    reqs = {"a": (pa, [5, 9, 9, 40], [], 0, 1), "b": (pb, [1, 2, 3], [], 2, 1), "c": (plain, [7], [], -1, 0)}
+    for step in range(12):
+        if step == 6:  # "a" ends; its slot goes to a new request with another prompt
+            reqs["a"] = (pa, [60, 61, 5], [], 0, 2)
+        logits = torch.randn(len(reqs), V, generator=g)
+        logits[:, [5, 9, 40, 60, 1, 2]] += 3.0  # tokens that penalties will have to push down
+        rows_s = [SampleRow(p, out, prompt, 0, slot=slot, epoch=ep) for p, prompt, out, slot, ep in reqs.values()]
+        rows_h = [SampleRow(p, out, prompt, 0) for p, prompt, out, _, _ in reqs.values()]
+        la, lb = logits.clone(), logits.clone()
+        ta = with_state.sample(la, rows_s).token_ids
+        tb = without.sample(lb, rows_h).token_ids
+        assert ta == tb and torch.equal(la, lb)
+        assert not torch.equal(la[0], logits[0]) and torch.equal(la[2], logits[2])
+        for (_, _, out, _, _), t in zip(reqs.values(), ta):
+            out.append(t)

@@ -77,6 +77,29 @@ def test_seeded_sampling_is_the_same_alone_and_in_a_busy_batch(sharp_dirs, dtype
     assert len(set(want)) > 1
 
 
+def test_penalties_bans_and_logprobs_with_and_without_graphs(sharp_dirs):
+    """Rows that need more than the sampling kernel replay the step up to the logits and are
+    sampled outside the capture: same tokens and log-probabilities as without graphs, and the
+    penalties do change what is generated."""
+    from llmserve_b200 import SamplingParams
+
+    sps = [SamplingParams(temperature=0.0, repetition_penalty=1.8, presence_penalty=0.4,
+                          frequency_penalty=0.3, max_tokens=30, ignore_eos=True),
+           SamplingParams(temperature=0.0, logprobs=3, max_tokens=30, ignore_eos=True),
+           SamplingParams(temperature=0.9, top_p=0.9, seed=5, min_tokens=8, max_tokens=30)]
+    runs = {}
+    for graphs in (True, False):
+        out = llm(sharp_dirs["C"], "C", "float32", cuda_graphs=graphs).generate(PROMPTS[:3], sps)
+        runs[graphs] = out
+    for a, b in zip(runs[True], runs[False]):
+        assert a.outputs[0].token_ids == b.outputs[0].token_ids
+    lp_a, lp_b = runs[True][1].outputs[0].logprobs, runs[False][1].outputs[0].logprobs
+    assert lp_a is not None and len(lp_a) == 30
+    assert lp_a == pytest.approx(lp_b, abs=1e-4)
+    plain = llm(sharp_dirs["C"], "C", "float32").generate(PROMPTS[:1], greedy(30))[0].outputs[0].token_ids
+    assert runs[True][0].outputs[0].token_ids != plain
+
+
 def test_long_generation_with_graphs_matches_stepwise(sharp_dirs):
     """120 decode steps: contexts cross page edges and the number of context partitions changes."""
     a = llm(sharp_dirs["C"], "C", "float32", cuda_graphs=True).generate(PROMPTS[:2], greedy(120))

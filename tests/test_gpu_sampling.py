@@ -106,3 +106,34 @@ def test_penalties_ban_and_logsumexp(ops):
     ops.ban_tokens(a, row.cuda(), tok.cuda())
     assert torch.isinf(a[0, 4]) and torch.isinf(a[2, 49]) and torch.isfinite(a[1]).all()
     assert torch.allclose(ops.logsumexp(logits.cuda()).cpu(), torch.logsumexp(logits, -1), atol=1e-5)
+
+
+def test_token_state_penalties_match_the_listed_ones(ops):
+    """The dense penalties kernel reading a token state against the sparse one fed by lists."""
+    R, V, slots = 4, 1031, 6
+    g = torch.Generator().manual_seed(12)
+    logits = torch.randn(R, V, generator=g)
+    state = torch.zeros(slots, V, dtype=torch.int32)
+    slot_of = [4, 0, 5, 2]
+    prompts = [torch.randint(0, V, (50,), generator=g).tolist() for _ in range(R)]
+    outs = [torch.randint(0, 40, (30,), generator=g).tolist() for _ in range(R)]  # repeats
+    s, t, f = [], [], []
+    for r in range(R):
+        for x in set(prompts[r]):
+            s.append(slot_of[r]); t.append(x); f.append(1)
+        for x in outs[r]:
+            s.append(slot_of[r]); t.append(x); f.append(0)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    state_gpu = state.cuda()
+    ops.token_state_add(state_gpu, i32(s).cuda(), i32(t).cuda(), i32(f).cuda())
+    PlainOps().token_state_add(state, i32(s), i32(t), i32(f))
+    assert torch.equal(state_gpu.cpu(), state)
+    pres = torch.tensor([0.5, 0.0, 1.0, 0.2]); freq = torch.tensor([0.25, 1.0, 0.0, 0.1])
+    rep = torch.tensor([1.0, 1.3, 2.0, 0.8])
+    rows = i32([0, 1, 2, 3])
+    a = logits.clone().cuda()
+    ops.apply_penalties_dense(a, rows.cuda(), i32(slot_of).cuda(), pres.cuda(), freq.cuda(), rep.cuda(), state_gpu)
+    b = logits.clone()
+    PlainOps().apply_penalties_dense(b, rows, i32(slot_of), pres, freq, rep, state)
+    assert torch.allclose(a.cpu(), b, atol=1e-6)
+    assert not torch.equal(b, logits)

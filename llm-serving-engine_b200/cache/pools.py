@@ -4,6 +4,10 @@ Keys and values of a group live in one tensor ``[layers, 2, pages, kv_heads, pag
 head_dim]``: the rows of one (page, head) are contiguous (``page_tokens * head_dim`` elements), so
 a kernel that walks a request's context for one head reads whole contiguous runs. Fixed-size
 per-request state lives in ``[layers, max_requests, *shape]`` tensors, indexed by state slot.
+
+Every key/value tensor has one page more than the manager hands out, and every state tensor one
+slot more (``spare_page(group)``, ``spare_slot``): rows that only pad a captured batch to its fixed
+size write there, where no request ever reads.
 """
 
 from __future__ import annotations
@@ -65,15 +69,16 @@ class CachePools:
         self.kv_groups = list(kv_groups)
         self.state_groups = list(state_groups)
         self.num_pages = list(num_pages)
+        self.max_requests = max_requests
         self.kv = [
             torch.zeros(
-                len(g.cache_ids), 2, n, g.num_kv_heads, g.page_tokens, g.head_dim,
+                len(g.cache_ids), 2, n + 1, g.num_kv_heads, g.page_tokens, g.head_dim,
                 dtype=dtype, device=device,
             )
             for g, n in zip(self.kv_groups, self.num_pages)
         ]
         self.state = [
-            torch.zeros(len(g.cache_ids), max_requests, *g.shape, dtype=g.dtype, device=device)
+            torch.zeros(len(g.cache_ids), max_requests + 1, *g.shape, dtype=g.dtype, device=device)
             for g in self.state_groups
         ]
         self._where: dict[int, tuple[str, int, int]] = {}
@@ -93,6 +98,15 @@ class CachePools:
             t = self.kv[gi][li]
             return CacheView(gi, self.kv_groups[gi].page_tokens, t[0], t[1], None, writes)
         return CacheView(-1, 0, None, None, self.state[gi][li], writes)
+
+    def spare_page(self, group: int) -> int:
+        """A page of ``group`` that the manager never hands out."""
+        return self.num_pages[group]
+
+    @property
+    def spare_slot(self) -> int:
+        """A state slot that no request ever holds."""
+        return self.max_requests
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.kv + self.state)

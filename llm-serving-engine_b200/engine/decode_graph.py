@@ -7,6 +7,12 @@ replayed: per step the host fills one pinned buffer (token ids, positions, conte
 tables, sampling parameters), copies it to the device in one transfer, replays the graph (model
 forward and sampling kernel) and reads the sampled token ids back.
 
+A graph has a fixed batch size. So that a batch that shrinks or grows by one does not need a new
+capture each time, batches are padded to the next of a few sizes (1, 2, 3, 4, 6, 8, 12, 16, ...):
+a padding row is a one-token sequence at position 0 whose block table names the cache's spare
+page and whose state slot is the spare slot, so it reads and writes nothing that a request owns,
+costs next to nothing in the attention, and its sample is dropped.
+
 Rows that need more than the sampling kernel (penalties, banned tokens, log-probabilities) use a
 second capture of the same step that ends with the logits; the sampler then runs on them
 uncaptured. The model forward is replayed either way.
@@ -80,6 +86,17 @@ class _Graph:
         return self.h[self.off[name] : self.off[name] + B].view(dtype)
 
 
+def batch_sizes(limit: int) -> list[int]:
+    """1, 2, 3, 4, 6, 8, 12, 16, ... up to ``limit`` (which is always one of them)."""
+    out, b = [], 1
+    while b < limit:
+        out.append(b)
+        if b >= 2 and b + b // 2 < limit:
+            out.append(b + b // 2)
+        b *= 2
+    return out + [limit]
+
+
 class DecodeGraphs:
     def __init__(self, runner) -> None:
         self.runner = runner
@@ -87,13 +104,25 @@ class DecodeGraphs:
         self.pool = None
         groups = runner.manager.groups
         self.min_kv_heads = min((g.num_kv_heads for g in groups), default=1)
-        # host mirror of every live request's block tables, by state slot, grown page by page
+        slots = runner.manager.max_requests
+        self.sizes = batch_sizes(slots)
+        # host mirror of every live request's block tables, by state slot, grown page by page;
+        # the row after the last slot is the padding rows' table: the spare page
         self.mirror = [
-            np.zeros((runner.manager.max_requests, -(-runner.max_model_len // g.page_tokens)), np.int32)
+            np.zeros((slots + 1, -(-runner.max_model_len // g.page_tokens)), np.int32)
             for g in groups
         ]
-        self.mirror_len = np.zeros((len(groups), runner.manager.max_requests), dtype=np.int64)
-        self.mirror_epoch = np.zeros(runner.manager.max_requests, dtype=np.int64)
+        for gi in range(len(groups)):
+            self.mirror[gi][slots, :] = runner.pools.spare_page(gi)
+        self.mirror_len = np.zeros((len(groups), slots), dtype=np.int64)
+        self.mirror_epoch = np.zeros(slots, dtype=np.int64)
+
+    def padded(self, n: int) -> int:
+        """The captured batch size that serves ``n`` rows."""
+        for b in self.sizes:
+            if b >= n:
+                return b
+        return n
 
     @staticmethod
     def forward_usable(entries: Sequence[StepEntry], rows) -> bool:
@@ -144,6 +173,13 @@ class DecodeGraphs:
                 need = -(-(c + 1) // m.groups[gi].page_tokens)
                 if len(table) < need:
                     raise ValueError(f"request {e.rid!r}: block table has {len(table)} pages, needs {need}")
+        n = len(entries)
+        # padding rows: one token at position 0 of a sequence that lives on the spare page and slot
+        tok[n:] = 0
+        pos[n:] = 0
+        ctx[n:] = 1
+        slots[n:] = m.max_requests
+        first[n:] = 1
         if int(ctx.max()) > self.runner.max_model_len:
             raise ValueError("a sequence would outgrow max_model_len")
         v = self.runner.model.plan.vocab_size
@@ -151,14 +187,16 @@ class DecodeGraphs:
             raise ValueError(f"token ids must lie in [0, {v})")
         for gi, (o, w) in enumerate(g.table_off):
             g.h[o : o + B * w].reshape(B, w)[:] = self.mirror[gi][slots]
-        p = [r.params for r in rows]
-        g.hview("temperature", np.float32)[:] = [q.temperature for q in p]
-        g.hview("top_k")[:] = [q.top_k for q in p]
-        g.hview("top_p", np.float32)[:] = [q.top_p for q in p]
-        g.hview("min_p", np.float32)[:] = [q.min_p for q in p]
-        g.hview("draw")[:] = [r.draw_index for r in rows]
-        so = g.off["seed"]
-        g.h[so : so + 2 * B].view(np.uint64)[:] = [r.seed & 0xFFFFFFFFFFFFFFFF for r in rows]
+        if g.sampled:
+            p = [r.params for r in rows]
+            pad = [0] * (B - n)
+            g.hview("temperature", np.float32)[:] = [q.temperature for q in p] + pad  # 0: greedy
+            g.hview("top_k")[:] = [q.top_k for q in p] + pad
+            g.hview("top_p", np.float32)[:] = [q.top_p for q in p] + [1.0] * (B - n)
+            g.hview("min_p", np.float32)[:] = [q.min_p for q in p] + pad
+            g.hview("draw")[:] = [r.draw_index for r in rows] + pad
+            so = g.off["seed"]
+            g.h[so : so + 2 * B].view(np.uint64)[:] = [r.seed & 0xFFFFFFFFFFFFFFFF for r in rows] + pad
         return int(ctx.max())
 
     def _forward(self, g: _Graph):
@@ -198,7 +236,8 @@ class DecodeGraphs:
         with the logits and the sampler runs on them before this method returns.
         """
         runner = self.runner
-        B = len(entries)
+        n = len(entries)
+        B = self.padded(n)
         simple = self.simple(rows)
         if not simple and (sampler is None or ahead_of is not None):
             raise ValueError("these rows need a sampler and cannot run ahead")
@@ -223,13 +262,13 @@ class DecodeGraphs:
         runner.ops.launches += g.launches
         runner.steps_run += 1
         if not simple:
-            return Pending(g, None, None, sampler.sample(g.logits, rows))
+            return Pending(g, None, None, n, sampler.sample(g.logits[:n], rows))
         buf = g.tokens_host[g.turn]
         g.turn ^= 1
         buf.copy_(g.tokens, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
-        return Pending(g, done, buf)
+        return Pending(g, done, buf, n)
 
     @staticmethod
     def collect(pending: "Pending"):
@@ -239,7 +278,7 @@ class DecodeGraphs:
         if pending.result is not None:
             return pending.result
         pending.done.synchronize()
-        return SamplerOutput(pending.tokens_host.tolist(), None, None)
+        return SamplerOutput(pending.tokens_host.tolist()[: pending.rows], None, None)
 
     def run(self, entries: Sequence[StepEntry], rows, sampler=None):
         return self.collect(self.launch(entries, rows, sampler=sampler))
@@ -248,5 +287,6 @@ class DecodeGraphs:
 class Pending:
     """A launched step whose sampled tokens have not been read yet (``result``: already sampled)."""
 
-    def __init__(self, graph: _Graph, done, tokens_host, result=None) -> None:
+    def __init__(self, graph: _Graph, done, tokens_host, rows: int, result=None) -> None:
         self.graph, self.done, self.tokens_host, self.result = graph, done, tokens_host, result
+        self.rows = rows  # rows of the batch that are requests (the rest pads the captured size)

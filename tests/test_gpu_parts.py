@@ -154,7 +154,8 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tiny_dirs):
     params["layers.0.mixer.w.weight"] = mix_w.cuda()
     model.bind(params)
     runner = ModelRunner(model, page_tokens=16, num_pages=24, max_model_len=256, max_num_seqs=4)
-    assert len(runner.pools.state) == 1 and runner.pools.state[0].shape == (1, 4, 64)
+    # four request slots and the spare one for rows that pad a captured batch
+    assert len(runner.pools.state) == 1 and runner.pools.state[0].shape == (1, 5, 64)
     assert len(runner.manager.groups) == 1 and runner.manager.groups[0].cache_ids == (1,)
     reqs = traces.make_requests([40, 23, 70, 9, 55, 31], 256, seed=13)
     pcfg, w = plain_llama.read_config(folder), plain_llama.read_weights(folder)

@@ -23,6 +23,8 @@
 //                 The scratch starts with LSE_ATTN_COUNTERS int counters (one per (sequence,
 //                 head group) is used), then the partial results; the counters must be zero
 //                 before a launch and are zero again after it.
+#include <type_traits>
+
 #include "attention_args.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -656,6 +658,245 @@ decode_split_kernel(const LseAttnArgs a, int page_shift) {
       a.num_splits, heads_here, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
 }
 
+#if LSE_HEAD_DIM == 64
+// ---------------------------------------------------------------------------- decode, grouped heads
+// Several query heads share one key/value head (grouped-query attention): the arithmetic per byte
+// of cache grows with the group, and one dot product per (key, head) on the CUDA cores no longer
+// keeps up with memory. Here the group's heads are the rows of a tensor-core tile
+// (mma.sync m16n8k16, bfloat16, float32 accumulation): per 16 keys a warp computes
+// S[heads x 16 keys] = Q K^T and O[heads x 64] += P V, whatever the size of the group (2..16).
+// Keys and values come straight from global memory in 16-byte pieces into the operand registers:
+//   * K as the "col" operand of Q K^T wants, per thread, pairs of neighbouring head dims of one
+//     key: which dims meet in which multiply is free as long as Q is laid out the same way, so
+//     thread (g, t) takes the 16-byte pieces t and t + 4 of key g's row;
+//   * V as the "col" operand of P V wants pairs of neighbouring *keys* for one dim: thread (g, t)
+//     loads piece g of the rows of its four keys (2t, 2t+1, 2t+8, 2t+9) and pairs them up with
+//     byte permutes. Column j of output tile g' is then head dim 8 g + j: a fixed permutation that
+//     is undone when the result is written.
+// Each warp keeps its own running maximum and sums; warps and context partitions are merged as
+// in the kernel above.
+constexpr int DM_HEADS = 16;
+
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_mma_kernel(const LseAttnArgs a, int page_shift) {
+  using T = bf16;
+  __shared__ float sm_m[DEC_WARPS][DM_HEADS], sm_l[DEC_WARPS][DM_HEADS];
+  __shared__ float sm_acc[DEC_WARPS][DM_HEADS][D];
+  pdl_trigger();
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = a.num_heads / a.num_kv_heads;
+  const int h0 = kvh * G;
+  const int seq = a.decode_seqs[b];
+  const int tok = a.cu_q[seq];
+  const int ctx = a.ctx_lens[seq];
+  const int k_first = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int span = ctx - k_first;
+  const int per = (span + a.num_splits - 1) / a.num_splits;
+  const int lo = k_first + split * per;
+  const int hi = min(ctx, lo + per);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const T* kp = (const T*)a.k_pages;
+  const T* vp = (const T*)a.v_pages;
+  const bool page_holds_tile = (a.page_tokens & 15) == 0;  // 16 aligned keys never straddle pages
+
+  pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
+
+  // Q as the row operand: rows g and g + 8 are heads h0 + g and h0 + g + 8 (zero beyond the
+  // group). Multiply step s pairs logical k = 2t, 2t+1, 2t+8, 2t+9 with the head dims
+  // d0, d0+1, d0+2, d0+3, d0 = 8 (t + 4 (s / 2)) + 4 (s % 2): the same dims that K supplies.
+  uint32_t qa[4][4];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int head = g + 8 * r;
+      uint32_t x0 = 0, x1 = 0;
+      if (head < G) {
+        const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + head) * D + d0;
+        x0 = *reinterpret_cast<const uint32_t*>(q);
+        x1 = *reinterpret_cast<const uint32_t*>(q + 2);
+      }
+      qa[s][r] = x0;      // a0 (row g) / a1 (row g + 8)
+      qa[s][2 + r] = x1;  // a2 / a3
+    }
+  }
+  float o[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // rows g and g + 8
+
+  auto row_base = [&](int key) -> size_t {  // offset of a key's row for this key/value head
+    int pi, off;
+    page_of(key, a.page_tokens, page_shift, pi, off);
+    return (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
+  };
+  if (hi > lo) {
+    const int first_tile = lo >> 4, last_tile = (hi - 1) >> 4;
+    for (int tile = first_tile + warp; tile <= last_tile; tile += DEC_WARPS) {
+      const int j0 = tile * 16;
+      // keys outside [lo, hi) are masked below; their rows are read from a key inside
+      auto inside = [&](int key) { return min(max(key, lo), hi - 1); };
+      size_t kb[2], vb[4];
+      if (page_holds_tile) {
+        const size_t page_row =
+            ((size_t)table[j0 >> page_shift] * a.num_kv_heads + kvh) * a.page_tokens;
+        const int mask = a.page_tokens - 1;
+        kb[0] = (page_row + (inside(j0 + g) & mask)) * D;
+        kb[1] = (page_row + (inside(j0 + g + 8) & mask)) * D;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          vb[i] = (page_row + (inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)) & mask)) * D;
+      } else {
+        kb[0] = row_base(inside(j0 + g));
+        kb[1] = row_base(inside(j0 + g + 8));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vb[i] = row_base(inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)));
+      }
+      uint4 kr[2][2], vr[4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        kr[nt][0] = *reinterpret_cast<const uint4*>(kp + kb[nt] + 8 * t);
+        kr[nt][1] = *reinterpret_cast<const uint4*>(kp + kb[nt] + 8 * (t + 4));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vr[i] = *reinterpret_cast<const uint4*>(vp + vb[i] + 8 * g);
+
+      // S = Q K^T for keys j0 + 8 nt + (2t, 2t+1); rows g and g + 8
+      float sc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const uint4 c = kr[nt][s >> 1];
+          const uint32_t b0 = (s & 1) ? c.z : c.x, b1 = (s & 1) ? c.w : c.y;
+          mma_bf16(sc[nt], qa[s], b0, b1);
+        }
+      }
+      float mx[2] = {m_run[0], m_run[1]};
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int key = j0 + 8 * nt + 2 * t + e;
+          const bool ok = key >= lo && key < hi;
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float v = ok ? sc[nt][2 * r + e] * a.scale : -INFINITY;
+            sc[nt][2 * r + e] = v;
+            mx[r] = fmaxf(mx[r], v);
+          }
+        }
+      float corr[2];
+      uint32_t pa[4];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_fin = (mx[r] == -INFINITY) ? 0.f : mx[r];
+        corr[r] = Exp<T>::f(m_run[r] - m_fin);
+        m_run[r] = mx[r];
+        float p[2][2], sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            p[nt][e] = Exp<T>::f(sc[nt][2 * r + e] - m_fin);
+            sum += p[nt][e];
+          }
+        l_run[r] = l_run[r] * corr[r] + sum;  // this thread's share of the row; joined at the end
+        pa[r] = pack_bf16(p[0][0], p[0][1]);      // a0 / a1: keys 2t, 2t+1
+        pa[2 + r] = pack_bf16(p[1][0], p[1][1]);  // a2 / a3: keys 2t+8, 2t+9
+      }
+      // O += P V; column g of output tile j is head dim 8 g + j
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j][0] *= corr[0];
+        o[j][1] *= corr[0];
+        o[j][2] *= corr[1];
+        o[j][3] *= corr[1];
+        const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+        const uint32_t v0 = j < 2 ? vr[0].x : j < 4 ? vr[0].y : j < 6 ? vr[0].z : vr[0].w;
+        const uint32_t v1 = j < 2 ? vr[1].x : j < 4 ? vr[1].y : j < 6 ? vr[1].z : vr[1].w;
+        const uint32_t v2 = j < 2 ? vr[2].x : j < 4 ? vr[2].y : j < 6 ? vr[2].z : vr[2].w;
+        const uint32_t v3 = j < 2 ? vr[3].x : j < 4 ? vr[3].y : j < 6 ? vr[3].z : vr[3].w;
+        mma_bf16(o[j], pa, __byte_perm(v0, v1, sel), __byte_perm(v2, v3, sel));
+      }
+    }
+  }
+  // this warp's result in shared memory, head dims back in their places
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int head = g + 8 * r;
+    if (head < G) {
+      if (t == 0) {
+        sm_m[warp][head] = m_run[r];
+        sm_l[warp][head] = l;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        sm_acc[warp][head][8 * (2 * t) + j] = o[j][2 * r];
+        sm_acc[warp][head][8 * (2 * t + 1) + j] = o[j][2 * r + 1];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps; one thread per (head, dim)
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int gq = idx / D, d = idx - gq * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][gq]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wt = (sm_m[w][gq] == -INFINITY) ? 0.f : Exp<T>::f(sm_m[w][gq] - M);
+      L += sm_l[w][gq] * wt;
+      A += sm_acc[w][gq][d] * wt;
+    }
+    const int h = h0 + gq;
+    if (a.num_splits == 1) {
+      T* op = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+      op[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+    } else {
+      float* part = a.scratch + LSE_ATTN_COUNTERS +
+                    (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
+      part[d] = A;
+      if (d == 0) {
+        part[D] = M;
+        part[D + 1] = L;
+      }
+    }
+  }
+  if (a.num_splits == 1) return;
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = reinterpret_cast<int*>(a.scratch) + (size_t)b * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(counter, 1);
+    is_last = (done == a.num_splits - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  merge_partitions<T, DM_HEADS>(
+      a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
+      a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
+}
+#endif  // LSE_HEAD_DIM == 64
+
 static int shift_of(int n) {
   if (n <= 0 || (n & (n - 1))) return -1;
   int s = 0;
@@ -674,6 +915,17 @@ template <typename T>
 static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
+#if LSE_HEAD_DIM == 64
+  if (std::is_same<T, bf16>::value && G >= 2 && G <= DM_HEADS && a->force_simt == 0) {
+    // grouped heads on the tensor cores: one block per (partition, key/value head, sequence)
+    dim3 mgrid(a->num_splits, a->num_kv_heads, a->num_decode);
+    if (mgrid.y > 65535 || mgrid.z > 65535) return LSE_BAD_ARGUMENT;
+    if (a->num_splits > 1 && (size_t)mgrid.y * mgrid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
+    if (a->num_splits > MERGE_SPLITS) return LSE_BAD_ARGUMENT;
+    launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+    return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  }
+#endif
   const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
   dim3 grid(a->num_splits, a->num_kv_heads * ((G + gt - 1) / gt), a->num_decode);
   if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;

@@ -895,6 +895,210 @@ decode_mma_kernel(const LseAttnArgs a, int page_shift) {
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
 }
+// The same for groups of up to 8 heads, with the roles turned: the 16 keys are the rows of the
+// tile and the heads its 8 columns, S^T = K Q^T and O^T = V^T P^T. No row of a tile is wasted on
+// heads that do not exist, so the accumulators take half the registers and more blocks fit an SM,
+// which is what hides the latency of the key/value loads. P^T comes out of S^T's accumulator
+// layout by one 8x8 transpose across the warp per eight keys (movmatrix).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
+  using T = bf16;
+  constexpr int HEADS = 8;
+  __shared__ float sm_m[DEC_WARPS][HEADS], sm_l[DEC_WARPS][HEADS];
+  __shared__ float sm_acc[DEC_WARPS][HEADS][D];
+  pdl_trigger();
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = a.num_heads / a.num_kv_heads;
+  const int h0 = kvh * G;
+  const int seq = a.decode_seqs[b];
+  const int tok = a.cu_q[seq];
+  const int ctx = a.ctx_lens[seq];
+  const int k_first = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int span = ctx - k_first;
+  const int per = (span + a.num_splits - 1) / a.num_splits;
+  const int lo = k_first + split * per;
+  const int hi = min(ctx, lo + per);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const T* kp = (const T*)a.k_pages;
+  const T* vp = (const T*)a.v_pages;
+  const bool page_holds_tile = (a.page_tokens & 15) == 0;  // 16 aligned keys never straddle pages
+
+  pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
+
+  // Q^T as the column operand: column g is head h0 + g (zero beyond the group); multiply step s
+  // pairs logical k = 2t, 2t+1, 2t+8, 2t+9 with head dims d0 .. d0+3, d0 = 8 (t + 4 (s / 2)) +
+  // 4 (s % 2), the dims that K's 16-byte pieces t and t + 4 supply.
+  uint32_t qb[4][2];
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
+    qb[s][0] = qb[s][1] = 0;
+    if (g < G) {
+      const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + g) * D + d0;
+      qb[s][0] = *reinterpret_cast<const uint32_t*>(q);
+      qb[s][1] = *reinterpret_cast<const uint32_t*>(q + 2);
+    }
+  }
+  // O^T: tile i, rows g and g + 8 are head dims 8 g + 2 i and 8 g + 2 i + 1; columns heads 2t, 2t+1
+  float ot[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2t and 2t + 1
+
+  auto row_base = [&](int key) -> size_t {
+    int pi, off;
+    page_of(key, a.page_tokens, page_shift, pi, off);
+    return (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
+  };
+  auto inside = [&](int key) { return min(max(key, lo), hi - 1); };  // masked keys read a valid row
+  if (hi > lo) {
+    const int first_tile = lo >> 4, last_tile = (hi - 1) >> 4;
+    for (int tile = first_tile + warp; tile <= last_tile; tile += DEC_WARPS) {
+      const int j0 = tile * 16;
+      size_t kb[2], vb[4];
+      if (page_holds_tile) {
+        const size_t page_row = ((size_t)table[j0 >> page_shift] * a.num_kv_heads + kvh) * a.page_tokens;
+        const int mask = a.page_tokens - 1;
+        kb[0] = (page_row + (inside(j0 + g) & mask)) * D;
+        kb[1] = (page_row + (inside(j0 + g + 8) & mask)) * D;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          vb[i] = (page_row + (inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)) & mask)) * D;
+      } else {
+        kb[0] = row_base(inside(j0 + g));
+        kb[1] = row_base(inside(j0 + g + 8));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) vb[i] = row_base(inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)));
+      }
+      uint4 kr[2][2], vr[4];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        kr[r][0] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * t);
+        kr[r][1] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * (t + 4));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vr[i] = *reinterpret_cast<const uint4*>(vp + vb[i] + 8 * g);
+
+      // S^T[keys g, g + 8][heads 2t, 2t+1]
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const uint4 c0 = kr[0][s >> 1], c1 = kr[1][s >> 1];
+        const uint32_t ka[4] = {(s & 1) ? c0.z : c0.x, (s & 1) ? c1.z : c1.x,
+                                (s & 1) ? c0.w : c0.y, (s & 1) ? c1.w : c1.y};
+        mma_bf16(sc, ka, qb[s][0], qb[s][1]);
+      }
+      const bool ok0 = j0 + g >= lo && j0 + g < hi, ok1 = j0 + g + 8 >= lo && j0 + g + 8 < hi;
+      float corr[2], p[2][2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float s0 = ok0 ? sc[e] * a.scale : -INFINITY;
+        const float s1 = ok1 ? sc[2 + e] * a.scale : -INFINITY;
+        float mx = fmaxf(m_run[e], fmaxf(s0, s1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_fin = (mx == -INFINITY) ? 0.f : mx;
+        corr[e] = Exp<T>::f(m_run[e] - m_fin);
+        m_run[e] = mx;
+        p[e][0] = Exp<T>::f(s0 - m_fin);
+        p[e][1] = Exp<T>::f(s1 - m_fin);
+        l_run[e] = l_run[e] * corr[e] + p[e][0] + p[e][1];  // this thread's share; joined at the end
+      }
+      // P^T[keys 2t, 2t+1 / 2t+8, 2t+9][head g] from P[key g / g + 8][heads 2t, 2t+1]
+      const uint32_t pb0 = movmatrix_trans(pack_bf16(p[0][0], p[1][0]));
+      const uint32_t pb1 = movmatrix_trans(pack_bf16(p[0][1], p[1][1]));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ot[i][0] *= corr[0];
+        ot[i][1] *= corr[1];
+        ot[i][2] *= corr[0];
+        ot[i][3] *= corr[1];
+        const uint32_t v0 = i == 0 ? vr[0].x : i == 1 ? vr[0].y : i == 2 ? vr[0].z : vr[0].w;
+        const uint32_t v1 = i == 0 ? vr[1].x : i == 1 ? vr[1].y : i == 2 ? vr[1].z : vr[1].w;
+        const uint32_t v2 = i == 0 ? vr[2].x : i == 1 ? vr[2].y : i == 2 ? vr[2].z : vr[2].w;
+        const uint32_t v3 = i == 0 ? vr[3].x : i == 1 ? vr[3].y : i == 2 ? vr[3].z : vr[3].w;
+        const uint32_t va[4] = {__byte_perm(v0, v1, 0x5410u), __byte_perm(v0, v1, 0x7632u),
+                                __byte_perm(v2, v3, 0x5410u), __byte_perm(v2, v3, 0x7632u)};
+        mma_bf16(ot[i], va, pb0, pb1);
+      }
+    }
+  }
+  // this warp's result in shared memory, head dims back in their places
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    float l = l_run[e];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    const int head = 2 * t + e;
+    if (head < G) {
+      if (g == 0) {
+        sm_m[warp][head] = m_run[e];
+        sm_l[warp][head] = l;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        sm_acc[warp][head][8 * g + 2 * i] = ot[i][e];
+        sm_acc[warp][head][8 * g + 2 * i + 1] = ot[i][2 + e];
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps; one thread per (head, dim)
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int gq = idx / D, d = idx - gq * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][gq]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wt = (sm_m[w][gq] == -INFINITY) ? 0.f : Exp<T>::f(sm_m[w][gq] - M);
+      L += sm_l[w][gq] * wt;
+      A += sm_acc[w][gq][d] * wt;
+    }
+    const int h = h0 + gq;
+    if (a.num_splits == 1) {
+      T* op = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+      op[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+    } else {
+      float* part = a.scratch + LSE_ATTN_COUNTERS +
+                    (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
+      part[d] = A;
+      if (d == 0) {
+        part[D] = M;
+        part[D + 1] = L;
+      }
+    }
+  }
+  if (a.num_splits == 1) return;
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = reinterpret_cast<int*>(a.scratch) + (size_t)b * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(counter, 1);
+    is_last = (done == a.num_splits - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  merge_partitions<T, HEADS>(
+      a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
+      a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
+}
 #endif  // LSE_HEAD_DIM == 64
 
 static int shift_of(int n) {
@@ -922,7 +1126,8 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     if (mgrid.y > 65535 || mgrid.z > 65535) return LSE_BAD_ARGUMENT;
     if (a->num_splits > 1 && (size_t)mgrid.y * mgrid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
     if (a->num_splits > MERGE_SPLITS) return LSE_BAD_ARGUMENT;
-    launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+    if (G <= 8) launch(decode_mma8_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+    else launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
     return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
   }
 #endif

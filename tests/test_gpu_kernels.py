@@ -243,6 +243,42 @@ def test_decode_split_counts_agree(ops, dtype, splits):
     close(got, ref, dtype, atol32=1e-5, rel16=0.02)
 
 
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("page", [8, 16, 32])  # 8: a tile of 16 keys straddles pages
+@pytest.mark.parametrize("nq,nk", [(2, 1), (6, 2), (4, 1), (5, 1), (8, 1), (12, 1), (16, 1), (32, 2)])
+def test_decode_of_grouped_heads(ops, nq, nk, page, window):
+    """Single tokens whose query heads share key/value heads, head size 64, bfloat16: groups of up
+    to 8 and of 9 to 16 heads take the two tensor-core kernels, a group of 1 the CUDA-core one.
+    Contexts that end inside a tile, start inside one (window, partitions), and of one token."""
+    ctx_lens = [1, 16, 17, 100, 333]
+    case = paged_case(5, [1] * 5, ctx_lens, nq, nk, 64, page, torch.bfloat16, seed=nq + page)
+    for splits in (1, 4):
+        got, ref, _ = run_attention(ops, case, nq, nk, 64, page, window, 512, splits=splits)
+        close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
+
+
+@pytest.mark.parametrize("group", [3, 8, 12])
+def test_grouped_decode_finds_one_far_key(ops, group):
+    """One key among 900 wins every head's softmax; the output must be its value row."""
+    nk, D, page, ctx = 2, 64, 16, 900
+    nq = nk * group
+    for far in (0, 15, 16, 450, 899):
+        case = list(paged_case(1, [1], [ctx], nq, nk, D, page, torch.bfloat16, seed=far))
+        qkv, k_pages, v_pages, tables = case[0], case[1], case[2], case[3]
+        q = torch.zeros(nq, D)
+        q[:, 3] = 6.0
+        qkv[0, : nq * D] = q.flatten().to(torch.bfloat16)
+        pg, off = int(tables[0, far // page]), far % page
+        if far == ctx - 1:  # the key of this step's token comes from the projection itself
+            k = torch.zeros(nk, D); k[:, 3] = 30.0
+            qkv[0, nq * D : (nq + nk) * D] = k.flatten().to(torch.bfloat16)
+        else:
+            k_pages[pg, :, off] = 0.0
+            k_pages[pg, :, off, 3] = 30.0
+        got, ref, _ = run_attention(ops, tuple(case), nq, nk, D, page, 0, 1024, splits=3, rope=False)
+        close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("far", [0, 15, 16, 700, 1023])
 def test_one_far_key_stands_out(ops, dtype, far):

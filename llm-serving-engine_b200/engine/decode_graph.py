@@ -280,6 +280,13 @@ class DecodeGraphs:
         pending.done.synchronize()
         return SamplerOutput(pending.tokens_host.tolist()[: pending.rows], None, None)
 
+    def collect_checked(self, pending: "Pending"):
+        """:meth:`collect`, then raise if a kernel of the step gave up a bounded wait (its results
+        would be wrong; the flag lives in host memory and is read once the step has finished)."""
+        out = self.collect(pending)
+        self.runner.ops.check_kernel_errors()
+        return out
+
     def run(self, entries: Sequence[StepEntry], rows, sampler=None):
         return self.collect(self.launch(entries, rows, sampler=sampler))
 

@@ -211,7 +211,7 @@ class ModelRunner:
         return pending
 
     def collect_decode(self, pending):
-        return self.decode_graphs.collect(pending)
+        return self.decode_graphs.collect_checked(pending)
 
     def step_and_sample(self, entries: Sequence[StepEntry], sampler, rows, graphs: bool = False):
         """A step followed by sampling on the device; only token ids come back to the host.
@@ -221,6 +221,13 @@ class ModelRunner:
         if graphs and self.can_launch_decode(entries, rows):
             return self.collect_decode(self.launch_decode(entries, rows, sampler=sampler))
         logits = self.step(entries)
-        out = sampler.sample(logits, rows)
+        out = sampler.sample(logits, rows)  # reads the tokens: the step has finished
         self.last_d2h_bytes = 4 * len(rows)
+        self.check_kernels()
         return out
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel recorded that it gave up a bounded wait. Call after a synchronisation."""
+        check = getattr(self.ops, "check_kernel_errors", None)
+        if check is not None:
+            check()

@@ -101,7 +101,7 @@ def build_host_step(entries: Sequence[StepEntry], manager, vocab_size: int, max_
     rows: list[int] = []
     for i, e in enumerate(entries):
         a, b = int(cu_q[i]), int(cu_q[i + 1])
-        token_ids[a:b] = np.asarray(e.tokens, dtype=np.int64)
+        token_ids[a:b] = e.tokens if isinstance(e.tokens, np.ndarray) else np.asarray(e.tokens, dtype=np.int64)
         positions[a:b] = np.arange(starts[i], starts[i] + q_lens[i], dtype=np.int32)
         token_seq[a:b] = i
         for w in e.want:

@@ -149,9 +149,12 @@ class ModelRunner:
             self._staging[idx] = (stage, ev)
         else:
             dev = torch.from_numpy(flat)
+        # one split instead of a slice per array; only arrays of rank 2 need a view on top
+        sizes = [offsets[i + 1] - offsets[i] for i in range(len(offsets) - 1)] + [total - offsets[-1]]
         got: dict[Any, torch.Tensor] = {}
-        for (name, a), off in zip(arrays, offsets):
-            got[name] = dev[off : off + a.size].view(a.shape)
+        for (name, a), piece in zip(arrays, dev.split(sizes)):
+            t = piece if piece.shape[0] == a.size else piece[: a.size]
+            got[name] = t if a.ndim == 1 else t.view(a.shape)
         plans = {
             key: {name: got[("plan", key, name)] for name in plan} for key, plan in plans_host.items()
         }

@@ -6,6 +6,8 @@ import enum
 import time
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from ..sampling.params import SamplingParams
 
 
@@ -39,6 +41,7 @@ class Sequence:
         self.output_text = ""
         self.detok_state = None
         self.seed = seed  # keys the device generator for this sequence
+        self._prompt_array = None
 
     @property
     def params(self) -> SamplingParams:
@@ -55,10 +58,17 @@ class Sequence:
     def token_ids(self) -> list[int]:
         return self.prompt_token_ids + self.output_token_ids
 
-    def tokens_from(self, start: int, n: int) -> list[int]:
+    def tokens_from(self, start: int, n: int):
+        """Tokens ``start .. start+n-1``. A portion of the prompt comes as a slice of one int32
+        array made once per sequence (a prompt is cut into portions many times; a list of a
+        few thousand Python ints would be converted each time)."""
         p = len(self.prompt_token_ids)
         if start + n <= p:
-            return self.prompt_token_ids[start : start + n]
+            if n < 16:
+                return self.prompt_token_ids[start : start + n]
+            if self._prompt_array is None:
+                self._prompt_array = np.asarray(self.prompt_token_ids, dtype=np.int32)
+            return self._prompt_array[start : start + n]
         if start >= p:
             return self.output_token_ids[start - p : start - p + n]
         return self.prompt_token_ids[start:] + self.output_token_ids[: start + n - p]

@@ -340,7 +340,7 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
 // ------------------------------------------------------------------ sampling
 void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k,
             const Tensor& top_p, const Tensor& min_p, const Tensor& seed, const Tensor& draw,
-            Tensor& out) {
+            Tensor& out, const OptTensor& scratch, int64_t which) {
   check_f32(logits, "logits");
   check_f32(temperature, "temperature");
   check_i32(top_k, "top_k");
@@ -355,10 +355,17 @@ void sample(const Tensor& logits, const Tensor& temperature, const Tensor& top_k
                   top_p.numel() == R && min_p.numel() == R && seed.numel() == R &&
                   draw.numel() == R && out.numel() == R,
               "sample: one parameter per row of logits is needed");
+  int* sc = nullptr;
+  int sc_rows = 0;
+  if (scratch) {  // several blocks per row for rows without a cut, if it was made for R rows or more
+    check_i32(*scratch, "scratch");
+    sc = scratch->data_ptr<int>();
+    sc_rows = (int)(scratch->numel() / (int64_t)lse_sample_scratch_ints(1));
+  }
   done(lse_sample(logits.data_ptr<float>(), R, (int)logits.size(1), temperature.data_ptr<float>(),
                   top_k.data_ptr<int>(), top_p.data_ptr<float>(), min_p.data_ptr<float>(),
                   reinterpret_cast<const uint64_t*>(seed.data_ptr<int64_t>()), draw.data_ptr<int>(),
-                  out.data_ptr<int>(), stream()),
+                  out.data_ptr<int>(), sc, sc_rows, (int)which, stream()),
        "sample");
 }
 
@@ -451,7 +458,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_q_tile", &attention_q_tile);
   m.def("attention_scratch_floats", &attention_scratch_floats);
   m.def("paged_attention", &paged_attention);
-  m.def("sample", &sample);
+  m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
+        py::arg("min_p"), py::arg("seed"), py::arg("draw"), py::arg("out"), py::arg("scratch") = py::none(),
+        py::arg("which") = 3);
+  m.def("sample_scratch_ints", [](int64_t rows) { return (int64_t)lse_sample_scratch_ints((int)rows); });
   m.def("logsumexp", &logsumexp);
   m.def("apply_penalties", &apply_penalties);
   m.def("ban_tokens", &ban_tokens);

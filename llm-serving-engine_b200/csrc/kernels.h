@@ -62,9 +62,16 @@ int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* o
 //   divided by its temperature, cut to top_k / top_p / min_p, and a token is drawn by the
 //   exponential race: argmax p_i / E_i, E_i ~ Exp(1) from a counter-based generator keyed by
 //   (seed[r], draw[r], i).
+//   scratch: lse_sample_scratch_ints(scratch_rows) ints, zero before the first launch (every
+//   launch leaves its counters zero), or null. With it (and scratch_rows >= R), rows that need no
+//   cut (and a temperature) are served by several blocks each. which: bit 0 = some row is greedy
+//   or has a cut, bit 1 = some row has a temperature and no cut; 3 if the caller does not know.
+//   A kernel whose rows are promised absent is not launched.
+size_t lse_sample_scratch_ints(int rows);
 int lse_sample(const float* logits, int R, int V, const float* temperature, const int* top_k,
                const float* top_p, const float* min_p, const uint64_t* seed, const int* draw,
-               int* out_tokens, cudaStream_t stream);
+               int* out_tokens, int* scratch, int scratch_rows, int which,
+               cudaStream_t stream);
 
 // out[r] = log(sum_i exp(logits[r, i]))
 int lse_logsumexp(const float* logits, int R, int V, float* out, cudaStream_t stream);

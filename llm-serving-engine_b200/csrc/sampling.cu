@@ -67,6 +67,97 @@ __device__ float block_max(float v, float* scratch) {
   return warp_max(lane < nw ? scratch[lane] : -INFINITY);
 }
 
+// ---- rows without a cut: several blocks per row -----------------------------------------------
+// Rows with a temperature but neither top-k, top-p nor min-p need one pass over the row and
+// nothing that all of it has to agree on first: the winner is the largest z_i - log(-log u_i),
+// and making the random numbers is most of the work. SAMPLE_CHUNKS blocks take a piece of the
+// row each; the block that finishes last picks the best of their results (ties: the lowest index,
+// as everywhere). Greedy rows stay with one block per row: reading the row once is too little
+// work to share (4.5 us alone against 4.9 shared at 8 rows, 4.6 against 7.9 at 64).
+constexpr int SAMPLE_CHUNKS = 8;
+constexpr int PAR_THREADS = 256;
+
+__device__ __forceinline__ bool row_is_parallel(float temp, int k, float p, float mp, int V) {
+  return temp >= 1e-5f && !((k > 0 && k < V) || p < 1.f) && !(mp > 0.f);
+}
+
+__global__ void __launch_bounds__(PAR_THREADS)
+sample_parallel_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
+                       const int* __restrict__ top_k, const float* __restrict__ top_p,
+                       const float* __restrict__ min_p, const uint64_t* __restrict__ seed,
+                       const int* __restrict__ draw, int* __restrict__ out,
+                       int* __restrict__ scratch, int scratch_rows) {
+  // scratch (made for scratch_rows rows): one counter per row, zero between launches, then per
+  // row SAMPLE_CHUNKS (value bits, index) pairs. The counters come first so that launches with
+  // different numbers of rows find them in the same place.
+  __shared__ ArgMax as[32];
+  __shared__ int is_last;
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x, c = blockIdx.y;
+  const float temp = temperature[r];
+  if (!row_is_parallel(temp, top_k[r], top_p[r], min_p[r], V)) return;
+  const float* row = logits + (size_t)r * V;
+  const int quads = (V + 3) >> 2;
+  const int per = (quads + SAMPLE_CHUNKS - 1) / SAMPLE_CHUNKS;  // groups of four entries per block
+  const int q_lo = c * per, q_hi = min(quads, q_lo + per);
+  const bool vec = (V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0;
+  const float inv_t = 1.f / temp;
+  const uint64_t sd = seed[r];
+  const uint32_t k0 = (uint32_t)sd, k1 = (uint32_t)(sd >> 32), dr = (uint32_t)draw[r];
+  ArgMax best = {-INFINITY, 0x7fffffff};
+  for (int q0 = q_lo + threadIdx.x; q0 < q_hi; q0 += 2 * PAR_THREADS) {
+    float v[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {  // two loads of a thread in flight
+      const int qd = q0 + u * PAR_THREADS;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[u][e] = -INFINITY;
+      if (qd < q_hi) {
+        if (vec) {
+          const float4 t = *reinterpret_cast<const float4*>(row + 4 * qd);
+          v[u][0] = t.x; v[u][1] = t.y; v[u][2] = t.z; v[u][3] = t.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (4 * qd + e < V) v[u][e] = row[4 * qd + e];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int qd = q0 + u * PAR_THREADS;
+      if (qd >= q_hi) continue;
+      uint32_t cn[4] = {(uint32_t)qd, dr, 0u, 0u};
+      philox4x32_10(cn, k0, k1);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (4 * qd + e >= V) continue;
+        const float u01 = ((float)(cn[e] >> 8) + 0.5f) * (1.f / 16777216.f);
+        best = better(best, ArgMax{v[u][e] * inv_t - logf(-logf(u01)), 4 * qd + e});
+      }
+    }
+  }
+  best = block_argmax(best, as);
+  int* counter = scratch + r;
+  int* pairs = scratch + scratch_rows + ((size_t)r * SAMPLE_CHUNKS + c) * 2;
+  if (threadIdx.x == 0) {
+    pairs[0] = __float_as_int(best.v);
+    pairs[1] = best.i;
+    __threadfence();
+    is_last = atomicAdd(counter, 1) == SAMPLE_CHUNKS - 1;
+  }
+  __syncthreads();
+  if (!is_last || threadIdx.x != 0) return;
+  __threadfence();
+  ArgMax win = {-INFINITY, 0x7fffffff};
+  const int* all = scratch + scratch_rows + (size_t)r * SAMPLE_CHUNKS * 2;
+  for (int j = 0; j < SAMPLE_CHUNKS; ++j)
+    win = better(win, ArgMax{__int_as_float(__ldcg(all + 2 * j)), __ldcg(all + 2 * j + 1)});
+  out[r] = win.i;
+  *counter = 0;
+}
+
 // ---- the cut of top-k / top-p --------------------------------------------------------------
 // With z = logit / temperature and e = exp(z - max z), element i is kept iff fewer than k elements
 // lie strictly above it and their mass (sum of e) is below top_p * (sum of all e). The cut is the
@@ -187,7 +278,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ min_p, const uint64_t* __restrict__ seed,
-              const int* __restrict__ draw, int* __restrict__ out) {
+              const int* __restrict__ draw, int* __restrict__ out, int parallel_rows) {
   extern __shared__ __align__(16) unsigned char sample_smem[];
   // histogram (counts, masses), later the candidate list (keys, masses); then the cached row
   int* h_cnt = reinterpret_cast<int*>(sample_smem);
@@ -203,6 +294,7 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * V;
   const float temp = temperature[r];
+  if (parallel_rows && row_is_parallel(temp, top_k[r], top_p[r], min_p[r], V)) return;
   if (temp < 1e-5f) {
     ArgMax a = {-INFINITY, 0x7fffffff};
     if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
@@ -421,8 +513,9 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
   auto kept = [&](float z) { return float_key(z) >= cut && z >= min_z && z >= floor_z; };
   auto score = [&](int i, float z, uint32_t bits) {
     const float u = ((float)(bits >> 8) + 0.5f) * (1.f / 16777216.f);  // (0, 1)
-    // argmax of p_i / E_i with E_i = -log(u): compare log p_i - log E_i
-    return ArgMax{z - zmax - logf(-logf(u)), i};
+    // argmax of p_i / E_i with E_i = -log(u): compare log p_i - log E_i; the normaliser of p is
+    // the same for every i and left out
+    return ArgMax{z - logf(-logf(u)), i};
   };
   bool listed = false;
   if (cut > 0 || mp > 0.f) {
@@ -549,12 +642,22 @@ __global__ void ban_kernel(float* __restrict__ logits, int V, const int* __restr
 
 using namespace lse;
 
+extern "C" size_t lse_sample_scratch_ints(int R) { return (size_t)R * (2 * SAMPLE_CHUNKS + 1); }
+
 extern "C" int lse_sample(const float* logits, int R, int V, const float* temperature,
                           const int* top_k, const float* top_p, const float* min_p,
-                          const uint64_t* seed, const int* draw, int* out_tokens,
-                          cudaStream_t stream) {
+                          const uint64_t* seed, const int* draw, int* out_tokens, int* scratch,
+                          int scratch_rows, int which, cudaStream_t stream) {
   if (R <= 0) return LSE_OK;
   if (V <= 0) return LSE_BAD_ARGUMENT;
+  // which: bit 0 = some row is greedy or has a cut (one block per row), bit 1 = some row has a
+  // temperature and no cut (several blocks per row, needs the scratch); a caller that does not
+  // know passes 3. Without scratch the one-block kernel serves every row.
+  const int parallel = (scratch != nullptr && scratch_rows >= R && R <= 65535) ? 1 : 0;
+  if (parallel && (which & 2))
+    launch(sample_parallel_kernel, dim3(R, SAMPLE_CHUNKS), PAR_THREADS, 0, stream, logits, V, temperature,
+           top_k, top_p, min_p, seed, draw, out_tokens, scratch, scratch_rows);
+  if (parallel && !(which & 1)) return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
   // histogram / candidate list, and the row itself when it fits beside them
   const size_t base = (size_t)HIST_BINS * 12;
   const size_t cached = base + (size_t)V * 4;
@@ -570,10 +673,10 @@ extern "C" int lse_sample(const float* logits, int R, int V, const float* temper
   }
   if (cached <= (size_t)max_smem - 4096)
     launch(sample_kernel<true>, R, SAMPLE_THREADS, cached, stream, logits, V, temperature, top_k, top_p,
-           min_p, seed, draw, out_tokens);
+           min_p, seed, draw, out_tokens, (parallel && (which & 2)) ? 1 : 0);
   else
     launch(sample_kernel<false>, R, SAMPLE_THREADS, base, stream, logits, V, temperature, top_k, top_p,
-           min_p, seed, draw, out_tokens);
+           min_p, seed, draw, out_tokens, (parallel && (which & 2)) ? 1 : 0);
   return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 

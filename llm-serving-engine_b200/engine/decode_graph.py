@@ -28,14 +28,17 @@ from typing import Sequence
 import numpy as np
 import torch
 
+from ..sampling.sampler import sample_kinds
 from .batch import DeviceStep, StepEntry
 
 
 class _Graph:
-    def __init__(self, owner: "DecodeGraphs", batch: int, splits: int, sampled: bool = True) -> None:
+    def __init__(self, owner: "DecodeGraphs", batch: int, splits: int, sampled: bool = True,
+                 kinds: int = 3) -> None:
         runner = owner.runner
         self.batch = B = batch
         self.sampled = sampled  # the capture ends with the sampling kernel (else with the logits)
+        self.kinds = kinds  # which sampling kernels the capture holds (see CudaOps.sample)
         dev = runner.device
         widths = [-(-runner.max_model_len // g.page_tokens) for g in runner.manager.groups]
         # layout of the per-step buffer, in int32 words
@@ -100,7 +103,7 @@ def batch_sizes(limit: int) -> list[int]:
 class DecodeGraphs:
     def __init__(self, runner) -> None:
         self.runner = runner
-        self.graphs: dict[tuple[int, int, bool], _Graph] = {}
+        self.graphs: dict[tuple[int, int, bool, int], _Graph] = {}
         self.pool = None
         groups = runner.manager.groups
         self.min_kv_heads = min((g.num_kv_heads for g in groups), default=1)
@@ -202,7 +205,7 @@ class DecodeGraphs:
     def _forward(self, g: _Graph):
         runner = self.runner
         logits = runner.model.forward(g.step, runner.pools)
-        return runner.ops.sample(logits, *g.sample_args) if g.sampled else logits
+        return runner.ops.sample(logits, *g.sample_args, kinds=g.kinds) if g.sampled else logits
 
     def _capture(self, g: _Graph) -> None:
         ops = self.runner.ops
@@ -244,10 +247,12 @@ class DecodeGraphs:
         ahead = 0 if ahead_of is None else 1
         max_ctx = 1 + ahead + max(runner.manager.held[e.rid].computed for e in entries)
         splits = runner.ops.decode_splits(B, self.min_kv_heads, max_ctx)
-        key = (B, splits, simple)
+        # padding rows are greedy, so a padded batch always holds the one-block kernel
+        kinds = (sample_kinds(r.params for r in rows) | (1 if B > n else 0)) if simple else 0
+        key = (B, splits, simple, kinds)
         g = self.graphs.get(key)
         if g is None:
-            g = self.graphs[key] = _Graph(self, B, splits, simple)
+            g = self.graphs[key] = _Graph(self, B, splits, simple, kinds)
         if g.h2d_done is not None:
             g.h2d_done.synchronize()
         self._fill(g, entries, rows, ahead)

@@ -30,6 +30,8 @@ class CudaOps:
         self.ext = build.load_core()
         self._attn_loaded: set[int] = set()
         self._scratch: torch.Tensor | None = None
+        self._sample_scratch: torch.Tensor | None = None
+        self._sample_rows = 0
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.attention_kernel = 0  # 0: fastest available; 1: CUDA cores; 2: mma.sync (tests compare them)
         self.use_skinny_gemm = True
@@ -242,9 +244,19 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ sampling
-    def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw):
+    def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw, kinds=3):
+        """``kinds``: bit 0 = some row is greedy or cut by top-k / top-p / min-p, bit 1 = some row has
+        a temperature and no cut; the kernel of a kind that is promised absent is not launched."""
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        self.ext.sample(logits, temperature, top_k, top_p, min_p, seed, draw, out)
+        rows = logits.shape[0]
+        if self._sample_scratch is None or self._sample_rows < rows:
+            if not torch.cuda.is_current_stream_capturing():
+                # results of the blocks that share a row, and a counter per row (zero between launches)
+                self._sample_rows = max(rows, 1024)
+                self._sample_scratch = torch.zeros(int(self.ext.sample_scratch_ints(self._sample_rows)),
+                                                   dtype=torch.int32, device=self.device)
+        scratch = self._sample_scratch if self._sample_rows >= rows else None
+        self.ext.sample(logits, temperature, top_k, top_p, min_p, seed, draw, out, scratch, kinds)
         self.launches += 1
         return out
 

@@ -56,6 +56,11 @@ class SamplingParams:
         return self.temperature < 1e-5
 
     @property
+    def has_cut(self) -> bool:
+        """A sampled row whose candidates are cut by top-k, top-p or min-p (never a greedy row)."""
+        return not self.greedy and (self.top_k > 0 or self.top_p < 1.0 or self.min_p > 0.0)
+
+    @property
     def has_penalties(self) -> bool:
         return (self.presence_penalty != 0 or self.frequency_penalty != 0
                 or self.repetition_penalty != 1.0)

@@ -86,7 +86,8 @@ class Sampler:
         if not want_lp and all(
             r.params.greedy and not r.params.has_penalties and not r.banned_token_ids for r in rows
         ):
-            return SamplerOutput(self.ops.sample(logits, *self._greedy(len(rows))).tolist(), None, None)
+            return SamplerOutput(
+                self.ops.sample(logits, *self._greedy(len(rows)), kinds=1).tolist(), None, None)
         pen = [(i, r) for i, r in enumerate(rows) if r.params.has_penalties]
         ban = [(i, t) for i, r in enumerate(rows) for t in r.banned_token_ids]
         # log-probabilities are those of the model, before penalties and bans change the logits
@@ -122,6 +123,7 @@ class Sampler:
             self._dev([q.min_p for q in p], torch.float32),
             self._dev([_as_int64(r.seed) for r in rows], torch.int64),
             self._dev([r.draw_index for r in rows], torch.int32),
+            kinds=sample_kinds(p),
         )
         if not want_lp:
             return SamplerOutput(tokens.tolist(), None, None)
@@ -183,6 +185,14 @@ class Sampler:
             self._dev([r.params.frequency_penalty for _, r in pen], torch.float32),
             self._dev([r.params.repetition_penalty for _, r in pen], torch.float32),
             self._token_state)
+
+
+def sample_kinds(params) -> int:
+    """Which of the two sampling kernels a batch needs (see ``CudaOps.sample``)."""
+    kinds = 0
+    for q in params:
+        kinds |= 1 if (q.greedy or q.has_cut) else 2
+    return kinds
 
 
 def _as_int64(seed: int) -> int:

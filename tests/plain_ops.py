@@ -134,7 +134,7 @@ class PlainOps:
         return out.view(T, num_heads * D).to(qkv.dtype)
 
     # ------------------------------------------------------------------ sampling
-    def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw):
+    def sample(self, logits, temperature, top_k, top_p, min_p, seed, draw, kinds=3):
         R, V = logits.shape
         out = torch.empty(R, dtype=torch.int32)
         for r in range(R):
@@ -165,7 +165,7 @@ class PlainOps:
             )
             bits = np.stack(c, axis=1).reshape(-1)[:V].astype(np.uint32)
             u = ((bits >> 8).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
-            score = (z - zmax) - torch.from_numpy(np.log(-np.log(u))).float()
+            score = z - torch.from_numpy(np.log(-np.log(u))).float()
             score[~keep] = float("-inf")
             out[r] = int(score.argmax())
         return out
@@ -211,7 +211,7 @@ class PlainOps:
             )
             bits = np.stack(c, axis=1).reshape(-1)[:V].astype(np.uint32)
             u = ((bits >> 8).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
-            score = (z - zmax) - torch.from_numpy(np.log(-np.log(u))).float()
+            score = z - torch.from_numpy(np.log(-np.log(u))).float()
             score[~keep] = float("-inf")
             out[r] = int(score.argmax())
         return out

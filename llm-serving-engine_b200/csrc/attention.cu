@@ -24,9 +24,9 @@
 //                 head group) is used), then the partial results; the counters must be zero
 //                 before a launch and are zero again after it. One dot product per key and
 //                 head on the CUDA cores: float32, and head sizes other than 64.
-//   decode_mma8 / decode_mma  single rows, bfloat16, head size 64: the same partitions and merge
-//                 with mma.sync tensor-core tiles (keys x heads for up to 8 heads per key/value
-//                 head, heads x keys for 9 to 16).
+//   decode_mma8 / decode_mma  single rows, bfloat16: the same partitions and merge with mma.sync
+//                 tensor-core tiles: keys x heads for up to 8 heads per key/value head (head
+//                 sizes 64 and 128), heads x keys for 9 to 16 (head size 64).
 #include <type_traits>
 
 #include "attention_args.h"
@@ -899,7 +899,11 @@ decode_mma_kernel(const LseAttnArgs a, int page_shift) {
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
 }
-// The same for groups of up to 8 heads, with the roles turned: the 16 keys are the rows of the
+#endif  // LSE_HEAD_DIM == 64
+
+#if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
+constexpr bool kHasDecodeMma8 = true;
+// For groups of up to 8 heads (head sizes 64 and 128), with the roles turned: the 16 keys are the rows of the
 // tile and the heads its 8 columns, S^T = K Q^T and O^T = V^T P^T. No row of a tile is wasted on
 // heads that do not exist, so the accumulators take half the registers and more blocks fit an SM,
 // which is what hides the latency of the key/value loads. P^T comes out of S^T's accumulator
@@ -914,6 +918,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   using T = bf16;
   constexpr int HEADS = 8;
+  constexpr int KCH = D / 32;  // 16-byte pieces of a key row per thread: pieces t, t + 4, ...
+  constexpr int KS = D / 16;   // multiply steps of K Q^T
+  constexpr int VCH = D / 64;  // 16-byte pieces of a value row per thread: pieces g, g + 8
+  constexpr int MT = D / 16;   // output tiles of 16 head dims
   __shared__ float sm_m[DEC_WARPS][HEADS], sm_l[DEC_WARPS][HEADS];
   __shared__ float sm_acc[DEC_WARPS][HEADS][D];
   pdl_trigger();
@@ -942,9 +950,9 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   // Q^T as the column operand: column g is head h0 + g (zero beyond the group); multiply step s
   // pairs logical k = 2t, 2t+1, 2t+8, 2t+9 with head dims d0 .. d0+3, d0 = 8 (t + 4 (s / 2)) +
   // 4 (s % 2), the dims that K's 16-byte pieces t and t + 4 supply.
-  uint32_t qb[4][2];
+  uint32_t qb[KS][2];
 #pragma unroll
-  for (int s = 0; s < 4; ++s) {
+  for (int s = 0; s < KS; ++s) {
     const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
     qb[s][0] = qb[s][1] = 0;
     if (g < G) {
@@ -953,10 +961,11 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
       qb[s][1] = *reinterpret_cast<const uint32_t*>(q + 2);
     }
   }
-  // O^T: tile i, rows g and g + 8 are head dims 8 g + 2 i and 8 g + 2 i + 1; columns heads 2t, 2t+1
-  float ot[4][4];
+  // O^T: tile i = 4 c + w (piece g + 8 c of the value rows, word w of the piece): rows g and g + 8
+  // are head dims 8 (g + 8 c) + 2 w and + 1; columns are heads 2t, 2t+1
+  float ot[MT][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
+  for (int i = 0; i < MT; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2t and 2t + 1
 
   auto row_base = [&](int key) -> size_t {
@@ -984,19 +993,22 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) vb[i] = row_base(inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)));
       }
-      uint4 kr[2][2], vr[4];
+      uint4 kr[2][KCH], vr[4][VCH];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        kr[r][0] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * t);
-        kr[r][1] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * (t + 4));
-      }
+      for (int r = 0; r < 2; ++r)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) vr[i] = *reinterpret_cast<const uint4*>(vp + vb[i] + 8 * g);
+        for (int c = 0; c < KCH; ++c)
+          kr[r][c] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * (t + 4 * c));
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < VCH; ++c)
+          vr[i][c] = *reinterpret_cast<const uint4*>(vp + vb[i] + 8 * (g + 8 * c));
 
       // S^T[keys g, g + 8][heads 2t, 2t+1]
       float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int s = 0; s < 4; ++s) {
+      for (int s = 0; s < KS; ++s) {
         const uint4 c0 = kr[0][s >> 1], c1 = kr[1][s >> 1];
         const uint32_t ka[4] = {(s & 1) ? c0.z : c0.x, (s & 1) ? c1.z : c1.x,
                                 (s & 1) ? c0.w : c0.y, (s & 1) ? c1.w : c1.y};
@@ -1023,15 +1035,16 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
       const uint32_t pb0 = movmatrix_trans(pack_bf16(p[0][0], p[1][0]));
       const uint32_t pb1 = movmatrix_trans(pack_bf16(p[0][1], p[1][1]));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < MT; ++i) {
         ot[i][0] *= corr[0];
         ot[i][1] *= corr[1];
         ot[i][2] *= corr[0];
         ot[i][3] *= corr[1];
-        const uint32_t v0 = i == 0 ? vr[0].x : i == 1 ? vr[0].y : i == 2 ? vr[0].z : vr[0].w;
-        const uint32_t v1 = i == 0 ? vr[1].x : i == 1 ? vr[1].y : i == 2 ? vr[1].z : vr[1].w;
-        const uint32_t v2 = i == 0 ? vr[2].x : i == 1 ? vr[2].y : i == 2 ? vr[2].z : vr[2].w;
-        const uint32_t v3 = i == 0 ? vr[3].x : i == 1 ? vr[3].y : i == 2 ? vr[3].z : vr[3].w;
+        const int c = i >> 2, w = i & 3;
+        const uint32_t v0 = w == 0 ? vr[0][c].x : w == 1 ? vr[0][c].y : w == 2 ? vr[0][c].z : vr[0][c].w;
+        const uint32_t v1 = w == 0 ? vr[1][c].x : w == 1 ? vr[1][c].y : w == 2 ? vr[1][c].z : vr[1][c].w;
+        const uint32_t v2 = w == 0 ? vr[2][c].x : w == 1 ? vr[2][c].y : w == 2 ? vr[2][c].z : vr[2][c].w;
+        const uint32_t v3 = w == 0 ? vr[3][c].x : w == 1 ? vr[3][c].y : w == 2 ? vr[3][c].z : vr[3][c].w;
         const uint32_t va[4] = {__byte_perm(v0, v1, 0x5410u), __byte_perm(v0, v1, 0x7632u),
                                 __byte_perm(v2, v3, 0x5410u), __byte_perm(v2, v3, 0x7632u)};
         mma_bf16(ot[i], va, pb0, pb1);
@@ -1052,9 +1065,10 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
         sm_l[warp][head] = l;
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        sm_acc[warp][head][8 * g + 2 * i] = ot[i][e];
-        sm_acc[warp][head][8 * g + 2 * i + 1] = ot[i][2 + e];
+      for (int i = 0; i < MT; ++i) {
+        const int dim = 8 * (g + 8 * (i >> 2)) + 2 * (i & 3);
+        sm_acc[warp][head][dim] = ot[i][e];
+        sm_acc[warp][head][dim + 1] = ot[i][2 + e];
       }
     }
   }
@@ -1103,7 +1117,9 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
 }
-#endif  // LSE_HEAD_DIM == 64
+#else
+constexpr bool kHasDecodeMma8 = false;
+#endif  // LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
 
 static int shift_of(int n) {
   if (n <= 0 || (n & (n - 1))) return -1;
@@ -1123,18 +1139,21 @@ template <typename T>
 static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   const int G = a->num_heads / a->num_kv_heads;
   const int ps = shift_of(a->page_tokens);
-#if LSE_HEAD_DIM == 64
-  if (std::is_same<T, bf16>::value && G <= DM_HEADS && a->force_simt == 0) {
-    // on the tensor cores: one block per (partition, key/value head, sequence). Also for a single
-    // head per key/value head: seven of the tile's eight columns are idle then, but the kernel
-    // still issues fewer instructions per key than a dot product on the CUDA cores (batch 8,
-    // 2176 keys: 27.1 us against 30.6; batch 64: 168 against 176).
+#if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
+  // On the tensor cores: one block per (partition, key/value head, sequence). Also for a single
+  // head per key/value head: seven of the tile's eight columns are idle then, but the kernel
+  // still issues fewer instructions per key than a dot product on the CUDA cores (head size 64,
+  // batch 8, 2176 keys: 27.1 us against 30.6; batch 64: 168 against 176).
+  constexpr int kMmaHeads = LSE_HEAD_DIM == 64 ? 16 : 8;  // 9..16 heads: head size 64 only
+  if (std::is_same<T, bf16>::value && G <= kMmaHeads && a->force_simt == 0) {
     dim3 mgrid(a->num_splits, a->num_kv_heads, a->num_decode);
     if (mgrid.y > 65535 || mgrid.z > 65535) return LSE_BAD_ARGUMENT;
     if (a->num_splits > 1 && (size_t)mgrid.y * mgrid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
     if (a->num_splits > MERGE_SPLITS) return LSE_BAD_ARGUMENT;
     if (G <= 8) launch(decode_mma8_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+#if LSE_HEAD_DIM == 64
     else launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+#endif
     return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
   }
 #endif

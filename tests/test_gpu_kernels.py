@@ -245,15 +245,18 @@ def test_decode_split_counts_agree(ops, dtype, splits):
 
 @pytest.mark.parametrize("window", [0, 37])
 @pytest.mark.parametrize("page", [8, 16, 32])  # 8: a tile of 16 keys straddles pages
-@pytest.mark.parametrize("nq,nk", [(2, 1), (6, 2), (4, 1), (5, 1), (8, 1), (12, 1), (16, 1), (32, 2)])
-def test_decode_of_grouped_heads(ops, nq, nk, page, window):
-    """Single tokens whose query heads share key/value heads, head size 64, bfloat16: groups of up
-    to 8 and of 9 to 16 heads take the two tensor-core kernels, a group of 1 the CUDA-core one.
-    Contexts that end inside a tile, start inside one (window, partitions), and of one token."""
+@pytest.mark.parametrize("nq,nk,D", [(2, 2, 64), (2, 1, 64), (6, 2, 64), (4, 1, 64), (5, 1, 64), (8, 1, 64),
+                                     (12, 1, 64), (16, 1, 64), (32, 2, 64),
+                                     (3, 3, 128), (8, 2, 128), (8, 1, 128), (12, 1, 128)])
+def test_decode_on_tensor_core_tiles(ops, nq, nk, D, page, window):
+    """Single tokens in bfloat16: up to 8 query heads per key/value head (head sizes 64 and 128)
+    and 9 to 16 heads (head size 64) take the two tensor-core kernels, 12 heads of size 128 the
+    CUDA-core one. Contexts that end inside a tile of 16 keys, start inside one (window,
+    partitions), and of one token."""
     ctx_lens = [1, 16, 17, 100, 333]
-    case = paged_case(5, [1] * 5, ctx_lens, nq, nk, 64, page, torch.bfloat16, seed=nq + page)
+    case = paged_case(5, [1] * 5, ctx_lens, nq, nk, D, page, torch.bfloat16, seed=nq + page)
     for splits in (1, 4):
-        got, ref, _ = run_attention(ops, case, nq, nk, 64, page, window, 512, splits=splits)
+        got, ref, _ = run_attention(ops, case, nq, nk, D, page, window, 512, splits=splits)
         close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
 
 

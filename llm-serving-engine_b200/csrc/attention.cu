@@ -705,7 +705,7 @@ decode_mma_kernel(const LseAttnArgs a, int page_shift) {
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
   const T* kp = (const T*)a.k_pages;
   const T* vp = (const T*)a.v_pages;
-  const bool page_holds_tile = (a.page_tokens & 15) == 0;  // 16 aligned keys never straddle pages
+  const bool page_holds_tile = page_shift >= 4;  // pages of 16, 32, ... tokens: a tile of 16 aligned keys lies in one
 
   pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
 
@@ -943,7 +943,7 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   const int* table = a.block_tables + (size_t)seq * a.table_stride;
   const T* kp = (const T*)a.k_pages;
   const T* vp = (const T*)a.v_pages;
-  const bool page_holds_tile = (a.page_tokens & 15) == 0;  // 16 aligned keys never straddle pages
+  const bool page_holds_tile = page_shift >= 4;  // pages of 16, 32, ... tokens: a tile of 16 aligned keys lies in one
 
   pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
 

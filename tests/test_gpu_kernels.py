@@ -244,7 +244,7 @@ def test_decode_split_counts_agree(ops, dtype, splits):
 
 
 @pytest.mark.parametrize("window", [0, 37])
-@pytest.mark.parametrize("page", [8, 16, 32])  # 8: a tile of 16 keys straddles pages
+@pytest.mark.parametrize("page", [8, 16, 32, 48])  # 8: a tile of 16 keys straddles pages; 48: no power of two
 @pytest.mark.parametrize("nq,nk,D", [(2, 2, 64), (2, 1, 64), (6, 2, 64), (4, 1, 64), (5, 1, 64), (8, 1, 64),
                                      (12, 1, 64), (16, 1, 64), (32, 2, 64),
                                      (3, 3, 128), (8, 2, 128), (8, 1, 128), (12, 1, 128)])

@@ -168,3 +168,24 @@ def test_penalties_from_the_token_state_equal_penalties_from_host_lists():
         assert not torch.equal(la[0], logits[0]) and torch.equal(la[2], logits[2])
         for (_, _, out, _, _), t in zip(reqs.values(), ta):
             out.append(t)
+
+
+def test_captured_batch_sizes_and_sampling_kinds():
+    from llmserve_b200.engine.decode_graph import batch_sizes
+    from llmserve_b200.sampling.params import SamplingParams
+    from llmserve_b200.sampling.sampler import sample_kinds
+
+    for limit in (1, 2, 5, 8, 64, 100, 256):
+        sizes = batch_sizes(limit)
+        assert sizes[0] == 1 and sizes[-1] == limit and sizes == sorted(set(sizes))
+        # padding never adds more than half of the rows again (a third from 4 rows on)
+        for n in range(1, limit + 1):
+            b = next(x for x in sizes if x >= n)
+            assert b <= max(n + 1, n * 3 // 2 + 1)
+    greedy = SamplingParams(temperature=0.0)
+    plain = SamplingParams(temperature=0.7)
+    cut = SamplingParams(temperature=0.7, top_p=0.9)
+    assert not greedy.has_cut and not plain.has_cut and cut.has_cut
+    assert not SamplingParams(temperature=0.0, top_k=5).has_cut  # greedy rows are never cut
+    assert sample_kinds([greedy]) == 1 and sample_kinds([plain]) == 2 and sample_kinds([cut]) == 1
+    assert sample_kinds([greedy, plain, cut]) == 3

@@ -2,8 +2,6 @@
 
 from __future__ import annotations
 
-import torch
-
 from conftest import TINY
 
 # Tolerances, fixed before the first GPU run.

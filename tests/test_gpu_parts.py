@@ -3,7 +3,6 @@ seen: registered, built into a model and stepped without a change to the framewo
 
 import dataclasses
 from dataclasses import dataclass
-from types import SimpleNamespace
 
 import numpy as np
 import pytest
@@ -11,7 +10,6 @@ import torch
 
 import plain_llama
 import traces
-from conftest import TINY
 
 pytestmark = pytest.mark.gpu
 

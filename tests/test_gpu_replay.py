@@ -1,10 +1,8 @@
 """The engine on the GPU against the plain implementation, for every way of cutting the work."""
 
 import json
-import struct
 import subprocess
 import sys
-from pathlib import Path
 
 import numpy as np
 import pytest

@@ -1,6 +1,5 @@
 """The sampling kernels against their plain versions and against the distributions they draw from."""
 
-import numpy as np
 import pytest
 import torch
 

@@ -144,7 +144,7 @@ def measure_decode(engine, batch, steps, warmup, seed):
     h2d, d2h = engine.runner.last_h2d_bytes, engine.runner.last_d2h_bytes
     # the same step, replayed back to back with no host in between
     graphs = engine.runner.decode_graphs.graphs
-    g = max((x for x in graphs.values() if x.batch == batch and x.graph is not None),
+    g = max((x for x in graphs.values() if x.batch == batch and x.slots == 0 and x.graph is not None),
             key=lambda x: x.step.decode_splits)
     for _ in range(3):
         g.graph.replay()

@@ -20,6 +20,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
+import numpy as np
+
 from .allocator import OutOfPages, PageAllocator
 
 RELEASED = -1
@@ -66,6 +68,18 @@ class _Held:
     computed: int = 0
     tables: list[list[int]] = field(default_factory=list)  # one per group
     epoch: int = 0  # number of the admission; a new holder of the same slot has another one
+    # the same tables as int32 arrays with room to grow (what a step's batch is built from)
+    arrays: list[np.ndarray] = field(default_factory=list)
+
+    def append_pages(self, g: int, pages: list[int]) -> None:
+        table = self.tables[g]
+        n = len(table)
+        table.extend(pages)
+        arr = self.arrays[g]
+        if len(table) > arr.shape[0]:
+            room = np.empty(max(len(table), 2 * arr.shape[0]), np.int32)
+            arr = self.arrays[g] = np.concatenate([arr, room])
+        arr[n : len(table)] = pages
 
 
 class CacheManager:
@@ -96,7 +110,8 @@ class CacheManager:
             raise OutOfPages("no free state slot")
         slot = self.free_slots.pop()
         self._epochs += 1
-        self.held[rid] = _Held(slot, 0, [[] for _ in self.groups], self._epochs)
+        self.held[rid] = _Held(slot, 0, [[] for _ in self.groups], self._epochs,
+                               [np.empty(16, np.int32) for _ in self.groups])
         return slot
 
     # ------------------------------------------------------------------ capacity
@@ -134,7 +149,25 @@ class CacheManager:
                     f"group {g}: request {rid!r} needs {k} pages, {self.pools[g].num_free} are free"
                 )
         for g, k in enumerate(need):
-            h.tables[g].extend(self.pools[g].allocate() for _ in range(k))
+            if k:
+                h.append_pages(g, [self.pools[g].allocate() for _ in range(k)])
+
+    def try_allocate(self, rid, n: int) -> bool:
+        """:meth:`allocate` for a live request if every group has the pages; else take nothing."""
+        h = self.held[rid]
+        end = h.computed + n
+        need = None
+        for g, spec in enumerate(self.groups):
+            k = -(-end // spec.page_tokens) - len(h.tables[g])
+            if k > 0:
+                if k > self.pools[g].num_free:
+                    return False
+                need = need or []
+                need.append((g, k))
+        if need:
+            for g, k in need:
+                h.append_pages(g, [self.pools[g].allocate() for _ in range(k)])
+        return True
 
     def commit(self, rid, n: int) -> None:
         """``n`` more tokens of ``rid`` are in the cache; give back pages a window has passed."""
@@ -151,6 +184,7 @@ class CacheManager:
                 if table[i] != RELEASED:
                     self.pools[g].release(table[i])
                     table[i] = RELEASED
+                    h.arrays[g][i] = RELEASED
                 i += 1
 
     def release(self, rid) -> None:
@@ -165,6 +199,11 @@ class CacheManager:
     # ------------------------------------------------------------------ queries
     def block_table(self, rid, group: int = 0) -> list[int]:
         return self.held[rid].tables[group]
+
+    def table_array(self, rid, group: int = 0) -> np.ndarray:
+        """The block table as an int32 array (a view: valid until the table next grows)."""
+        h = self.held[rid]
+        return h.arrays[group][: len(h.tables[group])]
 
     def state_slot(self, rid) -> int:
         return self.held[rid].slot
@@ -199,3 +238,4 @@ class CacheManager:
         for rid, h in self.held.items():
             for g, spec in enumerate(self.groups):
                 assert h.computed <= len(h.tables[g]) * spec.page_tokens, f"{rid!r}: table too short"
+                assert h.arrays[g][: len(h.tables[g])].tolist() == h.tables[g], f"{rid!r}: array differs"

@@ -74,19 +74,25 @@ def build_host_step(entries: Sequence[StepEntry], manager, vocab_size: int, max_
     if not entries:
         raise ValueError("a step needs at least one entry")
     n = len(entries)
-    q_lens = np.empty(n, dtype=np.int32)
-    starts = np.empty(n, dtype=np.int32)
-    slots = np.empty(n, dtype=np.int32)
-    seen = set()
-    for i, e in enumerate(entries):
-        if e.rid in seen:
-            raise ValueError(f"request {e.rid!r} appears twice in one step")
-        seen.add(e.rid)
-        if len(e.tokens) < 1:
-            raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
-        q_lens[i] = len(e.tokens)
-        starts[i] = manager.num_computed(e.rid)
-        slots[i] = manager.state_slot(e.rid)
+    held = []
+    for e in entries:
+        h = manager.held.get(e.rid)
+        if h is None:
+            raise KeyError(f"request {e.rid!r} is not live")
+        held.append(h)
+    if len({e.rid for e in entries}) != n:
+        seen = set()
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+    lens = [len(e.tokens) for e in entries]
+    if min(lens) < 1:
+        rid = entries[lens.index(min(lens))].rid
+        raise ValueError(f"request {rid!r}: an entry needs at least one token")
+    q_lens = np.asarray(lens, dtype=np.int32)
+    starts = np.asarray([h.computed for h in held], dtype=np.int32)
+    slots = np.asarray([h.slot for h in held], dtype=np.int32)
     cu_q = np.zeros(n + 1, dtype=np.int32)
     np.cumsum(q_lens, out=cu_q[1:])
     total = int(cu_q[-1])
@@ -95,41 +101,49 @@ def build_host_step(entries: Sequence[StepEntry], manager, vocab_size: int, max_
         raise ValueError(
             f"a sequence would reach {int(ctx_lens.max())} tokens; the engine was built for {max_positions}"
         )
-    token_ids = np.empty(total, dtype=np.int32)
-    positions = np.empty(total, dtype=np.int32)
-    token_seq = np.empty(total, dtype=np.int32)
+    if total == n:  # single tokens only
+        tokens64 = np.asarray([e.tokens[0] for e in entries], dtype=np.int64)
+    else:
+        tokens64 = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+    if tokens64.min() < 0 or tokens64.max() >= vocab_size:
+        raise ValueError(f"token ids must lie in [0, {vocab_size})")
+    token_seq = np.repeat(np.arange(n, dtype=np.int32), q_lens)
+    # a token's position: its row, minus its sequence's first row, plus the sequence's start
+    positions = np.arange(total, dtype=np.int32) + np.repeat(starts - cu_q[:-1], q_lens)
     rows: list[int] = []
     for i, e in enumerate(entries):
-        a, b = int(cu_q[i]), int(cu_q[i + 1])
-        token_ids[a:b] = e.tokens if isinstance(e.tokens, np.ndarray) else np.asarray(e.tokens, dtype=np.int64)
-        positions[a:b] = np.arange(starts[i], starts[i] + q_lens[i], dtype=np.int32)
-        token_seq[a:b] = i
         for w in e.want:
-            if not 0 <= w < q_lens[i]:
-                raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {q_lens[i]} tokens")
-            rows.append(a + int(w))
-    if token_ids.min() < 0 or token_ids.max() >= vocab_size:
-        raise ValueError(f"token ids must lie in [0, {vocab_size})")
+            if not 0 <= w < lens[i]:
+                raise ValueError(f"request {e.rid!r}: wanted place {w} is outside its {lens[i]} tokens")
+            rows.append(int(cu_q[i]) + int(w))
     tables = []
     for g, spec in enumerate(manager.groups):
-        need = -(-ctx_lens.astype(np.int64) // spec.page_tokens)
-        width = max(1, int(need.max()))
-        t = np.zeros((n, width), dtype=np.int32)
-        first_key = np.maximum(0, starts - spec.window + 1) if spec.window > 0 else np.zeros(n, np.int32)
-        for i, e in enumerate(entries):
-            tab = manager.block_table(e.rid, g)
-            if len(tab) < need[i]:
+        need = (-(-ctx_lens.astype(np.int64) // spec.page_tokens)).tolist()
+        t = np.zeros((n, max(1, max(need))), dtype=np.int32)
+        for i, h in enumerate(held):
+            k = need[i]
+            if len(h.tables[g]) < k:
                 raise ValueError(
-                    f"request {e.rid!r}: block table of group {g} has {len(tab)} pages, needs {int(need[i])}"
+                    f"request {entries[i].rid!r}: block table of group {g} has {len(h.tables[g])} pages, "
+                    f"needs {k}"
                 )
-            row = np.asarray(tab[: int(need[i])], dtype=np.int32)
-            lo = int(first_key[i]) // spec.page_tokens
-            if (row[lo:] < 0).any() or (row[lo:] >= manager.num_pages(g)).any():
-                raise ValueError(f"request {e.rid!r}: block table of group {g} names a page it does not hold")
-            t[i, : row.shape[0]] = np.maximum(row, 0)
+            t[i, :k] = h.arrays[g][:k]
+        if spec.window > 0:
+            # pages that the window has passed are given back (-1) and never read: the kernels start
+            # at the page of key ``start - window + 1``; all later entries must be pages held
+            first_page = np.maximum(0, starts - spec.window + 1) // spec.page_tokens
+            live = np.arange(t.shape[1])[None, :] >= first_page[:, None]
+            bad = ((t < 0) & live).any(axis=1)
+            np.maximum(t, 0, out=t)
+        else:
+            bad = (t < 0).any(axis=1)
+        bad |= (t >= manager.num_pages(g)).any(axis=1)
+        if bad.any():
+            rid = entries[int(np.argmax(bad))].rid
+            raise ValueError(f"request {rid!r}: block table of group {g} names a page it does not hold")
         tables.append(t)
     return HostStep(
-        token_ids=token_ids,
+        token_ids=tokens64.astype(np.int32),
         positions=positions,
         token_seq=token_seq,
         cu_q=cu_q,

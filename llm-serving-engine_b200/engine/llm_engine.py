@@ -38,6 +38,7 @@ class EngineConfig:
     seed: int = 0  # weights seed of "random:<alias>" models
     cuda_graphs: bool = True  # replay captured graphs for steps of single tokens only
     run_ahead: bool = True  # launch the next decode step before this one's tokens are read
+    warm_up: bool = True  # run a throw-away step at start-up (library handles, kernel modules)
     config_overrides: dict | None = None  # config.json keys to replace in a "random:<alias>" model
 
     def scheduler_config(self) -> SchedulerConfig:
@@ -130,6 +131,27 @@ class LLMEngine:
         self.last_step = StepStats()
         self.total_steps = 0
         self._pending: _InFlight | None = None  # a step launched ahead, not yet collected
+        if cfg.warm_up and self.runner.device.type == "cuda":
+            self._warm_up()
+
+    def _warm_up(self) -> None:
+        """One throw-away portion of a prompt (as long as the token budget, the size that a loaded
+        engine runs most) and one single token, sampled, on a request that is released again: the
+        first use of a process creates library handles and workspaces and loads kernel modules
+        (0.2 s and more), which would otherwise be the first request's wait."""
+        n = min(2048, self.cfg.max_num_batched_tokens, self.cfg.max_model_len - 2)
+        if n < 2 or not self.manager.fits_at_all(n + 1, n):
+            return
+        rid = ("warm-up",)
+        row = SampleRow(SamplingParams(temperature=0.0), [], [0], 0)
+        self.manager.admit(rid)
+        try:
+            for tokens in ([0] * n, [0]):
+                self.manager.allocate(rid, len(tokens))
+                self.runner.step_and_sample([StepEntry(rid, tokens, [len(tokens) - 1])], self.sampler, [row])
+                self.manager.commit(rid, len(tokens))
+        finally:
+            self.manager.release(rid)
 
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt: str | list[int], params: SamplingParams | None = None,
@@ -239,7 +261,7 @@ class LLMEngine:
         """Launch the step after ``cur`` before ``cur``'s tokens are known, if the batch cannot change."""
         if cur.pending is None or not self.cfg.run_ahead or self.scheduler.waiting:
             return None
-        if cur.pending.result is not None:  # sampled outside the graph: its tokens are on the host
+        if not cur.pending.feeds_next:  # sampled outside the graph, or rows in another order
             return None
         seqs = cur.sample_seqs
         if len(seqs) != len(cur.scheduled) or len(seqs) != len(self.scheduler.running):

@@ -195,22 +195,24 @@ class ModelRunner:
         """Give back everything ``rid`` holds."""
         self.manager.release(rid)
 
-    def can_launch_decode(self, entries: Sequence[StepEntry], rows) -> bool:
-        from .decode_graph import DecodeGraphs
-
-        return self.device.type == "cuda" and DecodeGraphs.forward_usable(entries, rows)
-
-    def launch_decode(self, entries: Sequence[StepEntry], rows, ahead_of=None, sampler=None):
-        """Enqueue a step of single tokens as a CUDA graph (see :meth:`DecodeGraphs.launch`);
-        :meth:`collect_decode` waits and returns the sampler's output. Rows with penalties, banned
-        tokens or log-probabilities need ``sampler`` and are sampled before this returns."""
+    def _graphs(self):
         from .decode_graph import DecodeGraphs
 
         if self.decode_graphs is None:
             self.decode_graphs = DecodeGraphs(self)
-        pending = self.decode_graphs.launch(entries, rows, ahead_of, sampler)
+        return self.decode_graphs
+
+    def can_launch_decode(self, entries: Sequence[StepEntry], rows) -> bool:
+        """Does this step run as a captured CUDA graph (see :meth:`DecodeGraphs.accepts`)?"""
+        return self.device.type == "cuda" and self._graphs().accepts(entries, rows)
+
+    def launch_decode(self, entries: Sequence[StepEntry], rows, ahead_of=None, sampler=None):
+        """Enqueue a step as a CUDA graph (see :meth:`DecodeGraphs.launch`);
+        :meth:`collect_decode` waits and returns the sampler's output. Rows with penalties, banned
+        tokens or log-probabilities need ``sampler`` and are sampled before this returns."""
+        pending = self._graphs().launch(entries, rows, ahead_of, sampler)
         self.last_h2d_bytes = 4 * pending.graph.words
-        self.last_d2h_bytes = 4 * len(entries)
+        self.last_d2h_bytes = 4 * len(rows)
         return pending
 
     def collect_decode(self, pending):

@@ -121,7 +121,7 @@ class Scheduler:
             n = min(remaining, budget) if chunked else remaining
             if n > budget and out.scheduled:
                 break
-            while not self.cm.can_allocate(seq.seq_id, n):
+            while not self.cm.try_allocate(seq.seq_id, n):
                 victim = self.running[-1]
                 if victim is seq:
                     self._preempt(seq, out)
@@ -130,7 +130,6 @@ class Scheduler:
                 self._preempt(victim, out)
             if seq is None:
                 break
-            self.cm.allocate(seq.seq_id, n)
             out.scheduled.append(ScheduledSeq(seq, n))
             budget -= n
             i += 1

@@ -81,6 +81,14 @@ class PagedAttention(Mixer):
     def plan_step(self, host_step, group):
         return self.ops.attention_plan(host_step, self.env.dtype, self.spec.head_dim)
 
+    def plan_rows(self, single: int, portions: int, tokens: int) -> dict[str, int]:
+        """Most rows of each work list for a step of ``single`` one-token sequences and ``portions``
+        longer ones that hold ``tokens`` tokens together. A captured step has lists of exactly this
+        many rows; a shorter list is filled up by repeating its last row (a tile that is computed
+        twice writes the same values twice)."""
+        qt = self.ops.attention_q_tile(self.env.dtype, self.spec.head_dim)
+        return {"tiles": tokens // qt + portions, "decode_seqs": single}
+
     accepts_residual = True
 
     def forward(self, h, step, cache, residual=None):

@@ -155,7 +155,10 @@ class Mixer(Part):
     ``cache_need()`` says what the mixer keeps per request (None for nothing).
     ``plan_step(host_step, group) -> dict[str, np.ndarray]`` may return int32 work lists that are
     the same for every layer with the same ``plan_key()``; the runner uploads them once per step
-    and hands them back in ``step.plans[plan_key()]``.
+    and hands them back in ``step.plans[plan_key()]``. A mixer with work lists whose steps should
+    also be captured as CUDA graphs when they hold portions of prompts gives the lists' largest
+    sizes with ``plan_rows(single, portions, tokens) -> dict[str, int]`` (see
+    ``PagedAttention.plan_rows``); without it such steps run uncaptured.
     """
 
     def cache_need(self):

@@ -96,6 +96,9 @@ class PlainOps:
             return qkv[:, : num_heads * D]
         return rot[:, :num_heads].to(out_dtype).reshape(T, num_heads * D)
 
+    def attention_q_tile(self, dtype, head_dim):
+        return self.q_tile
+
     def attention_plan(self, host_step, dtype, head_dim):
         tiles, decode = [], []
         for s, n in enumerate(host_step.q_lens.tolist()):

@@ -56,6 +56,27 @@ def test_tables_grow_by_pages_and_return_on_release():
         m.release("a")
 
 
+def test_try_allocate_takes_all_or_nothing():
+    m = CacheManager(groups(window=6), [6, 3], max_requests=2)
+    m.admit("a")
+    assert m.try_allocate("a", 8) and m.block_table("a") == [0, 1] and m.block_table("a", 1) == [0, 1]
+    assert m.table_array("a").tolist() == [0, 1]
+    assert m.try_allocate("a", 8)  # nothing new is needed
+    assert not m.try_allocate("a", 13)  # the second group has no fourth page: the first keeps its own
+    assert m.block_table("a") == [0, 1] and m.num_free_pages(0) == 4
+    m.commit("a", 8)
+    assert m.try_allocate("a", 1)
+    m.commit("a", 1)  # the next query reads keys 4 and later: the window group gives page 0 back
+    assert m.block_table("a", 1) == [RELEASED, 1, 2] and m.table_array("a", 1).tolist() == [RELEASED, 1, 2]
+    assert m.try_allocate("a", 4) and m.block_table("a", 1) == [RELEASED, 1, 2, 0]
+    m.check_invariants()
+    big = CacheManager(groups(), [100], max_requests=1)  # a table far longer than the array's first room
+    big.admit("x")
+    assert big.try_allocate("x", 4 * 70)
+    assert big.table_array("x").tolist() == big.block_table("x") == list(range(70))
+    big.check_invariants()
+
+
 def test_window_group_gives_pages_back_while_the_request_lives():
     m = CacheManager(groups(window=6), [20, 4], max_requests=1)
     m.admit("a")

@@ -189,3 +189,66 @@ def test_captured_batch_sizes_and_sampling_kinds():
     assert not SamplingParams(temperature=0.0, top_k=5).has_cut  # greedy rows are never cut
     assert sample_kinds([greedy]) == 1 and sample_kinds([plain]) == 2 and sample_kinds([cut]) == 1
     assert sample_kinds([greedy, plain, cut]) == 3
+
+
+def test_padded_batch_of_a_captured_step_with_portions(tiny_dirs):
+    """The batch that a captured step with portions of prompts runs (one-token rows first, padded;
+    then portion slots, the unused ones and the remaining tokens as padding sequences on the spare
+    page) gives the same logits as the step itself. Run here without a graph, on the CPU."""
+    import numpy as np
+    import torch
+
+    from llmserve_b200.engine.batch import DeviceStep, StepEntry
+    from llmserve_b200.engine.decode_graph import DecodeGraphs, row_bucket, slot_bucket, token_bucket
+
+    assert [token_bucket(n) for n in (1, 64, 65, 513, 1024, 1025, 2049)] == [64, 64, 128, 576, 1024, 1152, 2304]
+    assert [slot_bucket(n) for n in (1, 2, 8, 9)] == [8, 8, 8, 16]
+    assert [row_bucket(n, 8) for n in (0, 1, 4, 5, 8)] == [0, 4, 4, 8, 8] and row_bucket(17, 256) == 64
+    eng = engine(tiny_dirs["B"], "B", num_kv_blocks=200)
+    runner = eng.runner
+    graphs = DecodeGraphs(runner)
+    graphs.max_mixed_tokens = 4096
+    m = runner.manager
+    v = TINY["B"]["vocab_size"]
+    rng = np.random.default_rng(3)
+    # five requests with some history in the cache
+    history = {r: rng.integers(0, v, n).tolist() for r, n in zip("abcde", (7, 30, 1, 18, 44))}
+    runner.run([StepEntry(r, t, []) for r, t in history.items()])
+    # a step in the scheduler's order: single tokens and portions mixed; "c" unsampled, "f" new
+    entries = [StepEntry("a", [5], [0]), StepEntry("b", rng.integers(0, v, 37).tolist(), [36]),
+               StepEntry("c", [9], []), StepEntry("d", rng.integers(0, v, 2).tolist(), []),
+               StepEntry("e", [11], [0]), StepEntry("f", rng.integers(0, v, 70).tolist(), [69])]
+    m.admit("f")
+    for e in entries:
+        m.allocate(e.rid, len(e.tokens))
+    shape = graphs.mixed_shape(entries)
+    assert shape == (4, 8, 128)  # 3 single tokens -> 4; 3 portions -> 8 slots; 109 + 10 tokens -> 128
+    assert graphs.mixed_shape(entries[:1] + entries[2:3]) is None  # no portion: the decode graphs' case
+    assert graphs.mixed_shape([StepEntry("b", [1, 2, 3], [1])]) is None  # logits wanted inside a portion
+    want = runner.step(entries)
+    arrays, padded, index = graphs._fill_mixed(shape, entries)
+    plans = graphs._plans_mixed(shape, padded)
+    B, P, TP = shape
+    assert index == [0, 4, 2, 6] and padded.q_lens.tolist() == [1, 1, 1, 1, 37, 2, 70, 2, 2, 2, 2, 11]
+    assert arrays["positions"][B + 109 :].tolist() == [0, 1] * 4 + list(range(11))
+    spare = runner.pools.spare_page(0)
+    assert (arrays[("table", 0)][[3, 7, 11]] == spare).all() and (arrays["state_slots"][7:] == m.max_requests).all()
+    for key, (mixer, _) in runner.planners.items():
+        rows = mixer.plan_rows(B, P, TP)
+        assert {n: a.shape[0] for n, a in plans[key].items()} == rows
+        assert plans[key]["decode_seqs"].tolist() == [0, 1, 2, 3]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    step = DeviceStep(
+        token_ids=t(arrays["token_ids"]), positions=t(arrays["positions"]), token_seq=t(arrays["token_seq"]),
+        cu_q=t(arrays["cu_q"]), ctx_lens=t(arrays["ctx_lens"]), state_slots=t(arrays["state_slots"]),
+        first_portion=t(arrays["first_portion"]), block_tables=[t(arrays[("table", 0)])],
+        logit_rows=t(arrays["logit_rows"]), num_tokens=B + TP, num_seqs=B + P, num_logit_rows=B + P,
+        max_decode_ctx=0, decode_splits=1,
+        plans={k: {n: t(a) for n, a in p.items()} for k, p in plans.items()},
+    )
+    got = runner.model.forward(step, runner.pools)
+    assert got.shape[0] == B + P
+    torch.testing.assert_close(got[index], want, atol=1e-6, rtol=0)
+    # a shape is captured the second time it is asked for
+    rows = [None] * 4
+    assert not graphs.accepts(entries, rows) and graphs.accepts(entries, rows)

@@ -60,6 +60,43 @@ def test_graphs_portions_and_preemption_give_the_same_tokens(sharp_dirs):
     assert tight.engine.stats()["kernel_set"] == "cuda-sm100a"
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name):
+    """Steps that mix portions of prompts with single tokens, replayed as captured graphs of a
+    padded batch (one-token rows first, then portion slots; padding sequences on the spare page):
+    same tokens as the same steps run kernel by kernel. Greedy rows, a seeded temperature row (the
+    sampling kernel inside the capture) and, in a second run, a row with penalties (sampled outside
+    it, on rows gathered from the padded logits)."""
+    import numpy as np
+
+    from llmserve_b200 import SamplingParams
+
+    rng = np.random.default_rng(5)
+    v = TINY[name]["vocab_size"]
+    prompts = [rng.integers(0, v, n).tolist() for n in (70, 33, 5, 90, 17, 64, 2, 45, 120, 9)]
+    seeded = SamplingParams(temperature=0.8, top_p=0.9, seed=11, max_tokens=14, ignore_eos=True)
+    penal = SamplingParams(temperature=0.0, repetition_penalty=1.7, frequency_penalty=0.2, max_tokens=14,
+                           ignore_eos=True)
+    for special in (seeded, penal):
+        params = [greedy(10 + i) for i in range(len(prompts))]
+        params[3] = special
+        runs = {}
+        for graphs in (False, True):
+            m = llm(sharp_dirs[name], name, "float32", cuda_graphs=graphs, max_num_batched_tokens=24,
+                    num_kv_blocks=200)
+            if graphs:
+                m.engine.runner._graphs().capture_after = 1
+            runs[graphs] = [o.outputs[0].token_ids for o in m.generate(prompts, params)]
+            if graphs:
+                held = m.engine.runner.decode_graphs.graphs.values()
+                mixed = [g for g in held if g.slots > 0 and g.graph is not None]
+                assert len(mixed) >= 2 and any(g.batch > 0 for g in mixed)
+                assert any(not g.sampled for g in mixed) == (special is penal)
+                m.engine.manager.check_invariants()
+                assert m.engine.manager.usage() == 0.0
+        assert runs[True] == runs[False]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_seeded_sampling_is_the_same_alone_and_in_a_busy_batch(sharp_dirs, dtype):
     from llmserve_b200 import SamplingParams

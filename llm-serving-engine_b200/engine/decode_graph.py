@@ -222,11 +222,14 @@ class DecodeGraphs:
         # layer that runs; the device needs about 45 us per layer for its eleven kernels, however
         # few the tokens, plus 2 x weights x tokens / 0.8e15 s. The two meet at
         # tokens = 4.5e10 / (weights per layer); beyond that the step is bound by the device and
-        # padding would only make it longer.
+        # padding would only make it longer. Attention over long contexts is not in this estimate,
+        # so the count is capped where padding (a sixteenth at most) could cost more than the
+        # launches that are saved.
         model = runner.model
         matrix = sum(int(np.prod(d.shape)) for d in model.param_decls().values()
                      if d.role == "matrix" and len(d.shape) == 2 and d.shape[0] != model.plan.vocab_size)
-        self.max_mixed_tokens = max(128, int(len(model.plan.run_order) * 4.5e10 / max(matrix, 1)))
+        estimate = int(len(model.plan.run_order) * 4.5e10 / max(matrix, 1))
+        self.max_mixed_tokens = max(128, min(estimate, 1024))
         self.capture_after = 2  # a shape is captured the second time it is asked for
         self.asked: dict[tuple, int] = {}
         self.mixed_plannable = all(hasattr(m, "plan_rows") for m, _ in runner.planners.values())

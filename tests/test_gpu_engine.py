@@ -97,6 +97,56 @@ def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name):
         assert runs[True] == runs[False]
 
 
+def test_random_arrivals_give_the_same_tokens_with_and_without_graphs(sharp_dirs):
+    """Requests of every sampling kind arrive at random moments into a cache so small that some are
+    preempted; every step that can be captured is (decode steps, steps with portions, rows sampled
+    inside and outside the capture). Token for token the same as with every kernel launched alone."""
+    import random
+
+    from llmserve_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    def run(graphs):
+        eng = LLMEngine(EngineConfig(model=str(sharp_dirs["C"]), dtype="float32", block_size=32,
+                                     num_kv_blocks=26, max_model_len=1024, max_num_seqs=8,
+                                     max_num_batched_tokens=48, cuda_graphs=graphs))
+        if graphs:
+            eng.runner._graphs().capture_after = 1
+        rng = random.Random(4)
+        todo = []
+        for i in range(36):
+            kind, n_out = rng.random(), rng.randrange(2, 40)
+            if kind < 0.5:
+                sp = SamplingParams(temperature=0.0, max_tokens=n_out, ignore_eos=True)
+            elif kind < 0.8:
+                sp = SamplingParams(temperature=0.9, top_p=0.9, top_k=40, seed=i, max_tokens=n_out, ignore_eos=True)
+            elif kind < 0.9:
+                sp = SamplingParams(temperature=0.0, repetition_penalty=1.3, max_tokens=n_out, ignore_eos=True)
+            else:
+                sp = SamplingParams(temperature=0.7, seed=i, logprobs=2, max_tokens=n_out, ignore_eos=True)
+            todo.append(([rng.randrange(515) for _ in range(rng.choice([3, 17, 40, 90, 200]))], sp))
+        outs, steps = {}, 0
+        while todo or eng.has_unfinished_requests():
+            for _ in range(rng.randrange(0, 3)):
+                if todo:
+                    eng.add_request(*todo.pop(0))
+            for o in eng.step():
+                if o.finished:
+                    outs[o.request_id] = o.outputs[0].token_ids
+            steps += 1
+            if steps % 25 == 0:
+                eng.manager.check_invariants()
+        eng.manager.check_invariants()
+        assert eng.manager.usage() == 0.0
+        return outs, eng
+
+    plain, _ = run(False)
+    captured, eng = run(True)
+    assert len(plain) == 36 and captured == plain
+    held = eng.runner.decode_graphs.graphs.values()
+    assert sum(1 for g in held if g.slots) >= 3 and sum(1 for g in held if not g.slots) >= 3
+    assert eng.scheduler.num_preemptions > 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_seeded_sampling_is_the_same_alone_and_in_a_busy_batch(sharp_dirs, dtype):
     from llmserve_b200 import SamplingParams

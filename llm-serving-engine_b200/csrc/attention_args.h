@@ -48,6 +48,12 @@ int lse_attn_head_dim(void);
 // rows per tile that lse_attn_prefill expects in `tiles` for this dtype
 int lse_attn_q_tile(int dtype);
 size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, int num_splits);
+// The kernels of both launchers are enqueued with programmatic stream serialization and read the
+// batch description (`tiles`, `decode_seqs`, `cu_q`, `ctx_lens`) *before* their dependency wait.
+// Those four arrays must therefore be complete before the call is enqueued (a host-to-device copy
+// or an ordinary kernel earlier in the stream is), and must not be outputs of kernels of this
+// package that were launched the same way just before. q, the pages and the block tables are
+// read after the wait.
 int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream);
 int lse_attn_decode(const LseAttnArgs* a, cudaStream_t stream);
 
@@ -73,6 +79,8 @@ int lse_attn_decode(const LseAttnArgs* a, cudaStream_t stream);
 //    must start at zero, which holds because the buffer is zero when the library is loaded and
 //    every launch resets the counters it used. Two calls whose
 //    kernels overlap on the GPU (different streams) would race on it; run them one after the other.
+//  * The remembered address belongs to the device that is current at the call: `stream` must be
+//    a stream of that device. The rule above on `decode_seqs`, `cu_q` and `ctx_lens` holds here too.
 #define LSE_ATTN_NOALLOC_MAX_FLOATS (1 << 20)
 #define LSE_TOO_LARGE 3
 size_t lse_attn_decode_noalloc_max_floats(void);

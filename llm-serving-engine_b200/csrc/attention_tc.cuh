@@ -153,7 +153,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int k_end = pos0 + q0 + rows_here;  // one past the last key any row of the tile reads
   const int n_tiles = (k_end + KT - 1) / KT;
 
-  pdl_trigger();
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -182,6 +181,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+  // Dependents may become resident only now that this block holds its tensor memory: a dependent
+  // that allocated columns first and then sat in its dependency wait could keep this block
+  // waiting in tcgen05.alloc for ever.
+  pdl_trigger();
   pdl_wait();  // queries, keys and values were written by the kernel before this one
 
   if (warp == SOFTMAX_WARPS) {

@@ -571,6 +571,33 @@ class DecodeGraphs:
         self._fill(g, entries, rows, ahead)
         return self._replay(g, list(range(n)), rows, simple, sampler, ahead_of)
 
+    def captured_logits(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Float32 logits of a step of single tokens, run as a captured graph: what a check of
+        the captured path against the kernel-by-kernel path compares. Pages for the tokens must
+        have been allocated; nothing is committed."""
+        if not all(len(e.tokens) == 1 for e in entries):
+            raise ValueError("only a step of single tokens")
+        runner = self.runner
+        n = len(entries)
+        B = self.padded(n)
+        max_ctx = 1 + max(runner.manager.held[e.rid].computed for e in entries)
+        splits = runner.ops.decode_splits(B, self.min_kv_heads, max_ctx)
+        key = (B, splits, False, 0)
+        g = self.graphs.get(key)
+        if g is None:
+            g = self.graphs[key] = _Graph(self, B, splits, False, 0)
+        if g.h2d_done is not None:
+            g.h2d_done.synchronize()
+        self._fill(g, entries, [], 0)
+        g.dev.copy_(g.host, non_blocking=True)
+        g.h2d_done = torch.cuda.Event()
+        g.h2d_done.record()
+        if g.graph is None:
+            self._capture(g)
+        g.graph.replay()
+        runner.ops.launches += g.launches
+        return g.logits[:n].clone()
+
     @staticmethod
     def collect(pending: "Pending"):
         """The step's :class:`~llmserve_b200.sampling.sampler.SamplerOutput` (waits for it)."""

@@ -271,9 +271,10 @@ class LLMEngine:
         for seq in seqs:
             p = seq.params
             if (seq.is_finished or len(seq.output_token_ids) + 1 >= p.max_tokens
-                    or seq.num_tokens + 1 >= self.cfg.max_model_len
-                    or not self.manager.can_allocate(seq.seq_id, 2)):
+                    or seq.num_tokens + 1 >= self.cfg.max_model_len):
                 return None
+        if not self._pages_for_all(seqs, 2):
+            return None
         rows = [self._sample_row(seq, ahead=1) for seq in seqs]
         entries = [StepEntry(seq.seq_id, [0], [0]) for seq in seqs]
         from .decode_graph import DecodeGraphs
@@ -286,6 +287,17 @@ class LLMEngine:
         flight = _InFlight([(seq, 1) for seq in seqs], list(seqs), StepStats(), t0)
         flight.pending = self.runner.launch_decode(entries, rows, ahead_of=cur.pending)
         return flight
+
+    def _pages_for_all(self, seqs, n: int) -> bool:
+        """Are there pages for ``n`` more tokens of *every* one of ``seqs`` at once? The needs are
+        added up group by group: each sequence alone may fit while all of them together do not
+        (equal prompts cross a page's edge in the same step), and then the step is not launched
+        ahead, so that the scheduler can preempt in the next one."""
+        need = [0] * len(self.manager.groups)
+        for seq in seqs:
+            for g, k in enumerate(self.manager.pages_needed(seq.seq_id, n)):
+                need[g] += k
+        return all(k <= self.manager.num_free_pages(g) for g, k in enumerate(need))
 
     def _finish_step(self, cur: "_InFlight"):
         """Read the step's tokens and do the host's part. Returns (outputs, batch unchanged)."""

@@ -1,8 +1,9 @@
 """A plain, slow implementation of the Llama forward pass, written from the reference's formulas.
 
-Whole sequences, no cache, no batching, float32 (or float64) on the CPU, one function per part.
-It shares no code with the engine: it reads ``config.json`` with ``json`` and the weights with
-``safetensors`` by their checkpoint names.
+Whole sequences, no cache, no batching, float32 (or float64), one function per part. It runs on
+the CPU unless a test names another device for the models with real layer widths (the same plain
+torch operations, in float64, only faster). It shares no code with the engine: it reads
+``config.json`` with ``json`` and the weights with ``safetensors`` by their checkpoint names.
 
 It was compared once with the reference's own model code (``llmserve.models.transformer.CausalLM``
 imported on the CPU); the script and its small outputs are in ``tests/golden/``.
@@ -79,7 +80,8 @@ def rope_inverse_frequencies(head_dim, theta, scaling=None):
 
 def rope_tables(positions, head_dim, theta, scaling=None, dtype=torch.float32):
     """cos and sin ``[T, head_dim]`` (both halves alike), src/llmserve/models/layers.py:59-63."""
-    ang = torch.outer(positions.to(torch.float64), rope_inverse_frequencies(head_dim, theta, scaling))
+    inv = rope_inverse_frequencies(head_dim, theta, scaling).to(positions.device)
+    ang = torch.outer(positions.to(torch.float64), inv)
     emb = torch.cat([ang, ang], dim=-1)
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
@@ -102,8 +104,8 @@ def attention(q, k, v, scale, window=0):
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     s = torch.einsum("thd,shd->hts", q, k) * scale
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
+    i = torch.arange(T, device=q.device)[:, None]
+    j = torch.arange(T, device=q.device)[None, :]
     visible = j <= i
     if window > 0:
         visible &= (i - j) < window
@@ -146,16 +148,19 @@ def attention_block(h, w, prefix, cfg, positions, window=0, kv_from=None):
     return o, (k, v)
 
 
-def forward(cfg, w, token_ids, run_order=None, windows=None, dtype=torch.float32):
+def forward(cfg, w, token_ids, run_order=None, windows=None, dtype=torch.float32, device="cpu",
+            rows=None):
     """Logits ``[T, vocab]`` for one whole sequence (src/llmserve/models/transformer.py:125-139).
 
     run_order: list of (layer, cache id); default every layer once with its own cache. An entry
     whose cache id was filled by an earlier entry reads that entry's keys and values.
     windows: per layer attention window (0 = all), default none.
+    rows: positions whose logits are returned (default all; a large vocabulary times thousands of
+    positions would not fit). The result comes back on the CPU.
     """
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(ids.shape[0])
-    w = {k: v.to(dtype) for k, v in w.items()}
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=device)
+    positions = torch.arange(ids.shape[0], device=device)
+    w = {k: v.to(device=device, dtype=dtype) for k, v in w.items()}
     x = w["model.embed_tokens.weight"][ids]
     run_order = run_order or [(i, i) for i in range(cfg["layers"])]
     caches = {}
@@ -169,9 +174,11 @@ def forward(cfg, w, token_ids, run_order=None, windows=None, dtype=torch.float32
         h = rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
         x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
                        w[p + "mlp.down_proj.weight"])
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long, device=device)]
     x = rms_norm(x, w["model.norm.weight"], cfg["eps"])
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
-    return (x @ head.T).float() if dtype == torch.float32 else x @ head.T
+    return (x @ head.T).cpu()
 
 
 def model_logits(folder, token_ids, dtype=torch.float32, **kw):

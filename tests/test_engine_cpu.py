@@ -252,3 +252,24 @@ def test_padded_batch_of_a_captured_step_with_portions(tiny_dirs):
     # a shape is captured the second time it is asked for
     rows = [None] * 4
     assert not graphs.accepts(entries, rows) and graphs.accepts(entries, rows)
+
+
+def test_running_ahead_asks_for_the_pages_of_all_sequences_together(sharp_dirs):
+    """Equal prompts reach a page's edge in the same step. With fewer free pages than sequences
+    each of them alone could grow, all together cannot: the step must not be launched ahead."""
+    from llmserve_b200 import SamplingParams
+
+    pt = TINY["A"]["page_tokens"]
+    eng = engine(sharp_dirs["A"], "A", num_kv_blocks=4)  # three sequences of one page, one page free
+    sp = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
+    for _ in range(3):
+        eng.add_request(list(range(1, pt - 1)), sp)  # pt - 2 tokens: the second next token needs a page
+    eng.step()
+    seqs = list(eng.scheduler.running)
+    assert len(seqs) == 3 and eng.manager.num_free_pages(0) == 1
+    assert all(eng.manager.can_allocate(s.seq_id, 3) for s in seqs)  # each alone fits
+    assert not eng._pages_for_all(seqs, 3)
+    assert eng._pages_for_all(seqs[:1], 3) and eng._pages_for_all(seqs, 2)
+    done = run_all(eng)  # the scheduler preempts where pages run out; nothing raises
+    assert len(done) == 3 and eng.scheduler.num_preemptions > 0
+    assert len({tuple(o.outputs[0].token_ids) for o in done.values()}) == 1

@@ -1154,7 +1154,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
 #if LSE_HEAD_DIM == 64
     else launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
 #endif
-    return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+    return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
   }
 #endif
   const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
@@ -1165,7 +1165,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   if (gt == 1) launch(decode_split_kernel<T, 1>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   else if (gt == 2) launch(decode_split_kernel<T, 2>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
   else launch(decode_split_kernel<T, 4>, grid, DEC_WARPS * 32, 0, stream, *a, ps);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 }  // namespace lse
@@ -1214,7 +1214,7 @@ extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
     prefill_mma_kernel<<<grid, MMA_THREADS, smem, stream>>>(*a, ps);
 #endif
   }
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 // ---- no-allocation variant: scratch inside the library's device image ---------------------------

@@ -21,6 +21,7 @@ using OptTensor = std::optional<Tensor>;
 int dtype_code(const Tensor& t, const char* what) {
   if (t.scalar_type() == torch::kFloat32) return LSE_F32;
   if (t.scalar_type() == torch::kBFloat16) return LSE_BF16;
+  if (t.scalar_type() == torch::kInt64) return LSE_FIXED64;  // fixed-point sums of the few-rows product
   TORCH_CHECK(false, what, ": dtype must be float32 or bfloat16, got ", t.scalar_type());
 }
 
@@ -49,6 +50,13 @@ void done(int code, const char* what) {
   if (code != LSE_OK) {
     cudaError_t e = cudaGetLastError();
     TORCH_CHECK(false, what, ": launch failed: ", cudaGetErrorString(e));
+  }
+  // a capture that something has invalidated is reported where it is first seen, not at its end
+  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream(), &status) != cudaSuccess ||
+      status == cudaStreamCaptureStatusInvalidated) {
+    cudaGetLastError();
+    TORCH_CHECK(false, what, ": the stream's graph capture is invalid after this call");
   }
 }
 
@@ -97,7 +105,7 @@ void add_rmsnorm(Tensor& x, const OptTensor& residual, const Tensor& weight, dou
 Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tensor& positions,
                      const Tensor& token_seq, const OptTensor& cos, const OptTensor& sin,
                      const OptTensor& k_pages, const OptTensor& v_pages, const Tensor& block_tables,
-                     int64_t page_tokens, bool q_bf16, bool zero_in) {
+                     int64_t page_tokens, bool q_bf16) {
   check_cuda(qkv, "qkv");
   check_i32(positions, "positions");
   check_i32(token_seq, "token_seq");
@@ -108,7 +116,8 @@ Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tenso
   TORCH_CHECK(block_tables.dim() == 2, "rope_kv_write: block_tables must be [sequences, blocks]");
   const int in_code = dtype_code(qkv, "qkv");
   const int out_code = q_bf16 ? LSE_BF16 : LSE_F32;
-  TORCH_CHECK(in_code == out_code || in_code == LSE_F32, "rope_kv_write: bfloat16 qkv cannot give float32 q");
+  TORCH_CHECK(in_code == out_code || in_code == LSE_F32 || (in_code == LSE_FIXED64 && q_bf16),
+              "rope_kv_write: this qkv dtype cannot give this q dtype");
   const float *c = nullptr, *s = nullptr;
   if (cos) {
     TORCH_CHECK(sin.has_value(), "rope_kv_write: cos without sin");
@@ -138,19 +147,19 @@ Tensor rope_kv_write(Tensor& qkv, int64_t nq, int64_t nk, int64_t D, const Tenso
   done(lse_rope_kv_write(qkv.data_ptr(), in_code, q.data_ptr(), out_code, T, (int)nq, (int)nk, (int)D,
                          positions.data_ptr<int>(), token_seq.data_ptr<int>(), c, s, kp, vp,
                          block_tables.data_ptr<int>(), (int)block_tables.size(1), (int)page_tokens,
-                         zero_in ? 1 : 0, stream()),
+                         stream()),
        "rope_kv_write");
   return q;
 }
 
-void silu_mul(const Tensor& gu, Tensor& out, bool zero_in) {
+void silu_mul(const Tensor& gu, Tensor& out) {
   check_cuda(gu, "gu");
   check_cuda(out, "out");
   TORCH_CHECK(gu.dim() == 2 && out.dim() == 2 && gu.size(1) == 2 * out.size(1) &&
                   gu.size(0) == out.size(0),
               "silu_mul: gu must be [T, 2I] and out [T, I]");
   done(lse_silu_mul(gu.data_ptr(), dtype_code(gu, "gu"), out.data_ptr(), dtype_code(out, "out"),
-                    (int)gu.size(0), (int)out.size(1), zero_in ? 1 : 0, stream()),
+                    (int)gu.size(0), (int)out.size(1), stream()),
        "silu_mul");
 }
 
@@ -188,8 +197,8 @@ void clear_kernel_error() { *error_flag() = 0; }
 
 int64_t gemm_bf16_skinny_max_rows() { return lse_gemm_bf16_skinny_max_rows(); }
 
-void gemm_bf16_skinny(const Tensor& a, const Tensor& w, const OptTensor& bias, Tensor& out,
-                      bool atomic_add) {
+// out += a w^T (+ bias), out a buffer of fixed-point sums (int64)
+void gemm_bf16_skinny(const Tensor& a, const Tensor& w, const OptTensor& bias, Tensor& out) {
   check_cuda(a, "a");
   check_cuda(w, "w");
   check_cuda(out, "out");
@@ -205,10 +214,22 @@ void gemm_bf16_skinny(const Tensor& a, const Tensor& w, const OptTensor& bias, T
                 "gemm_bf16_skinny: bias must be bfloat16 [N]");
     b = bias->data_ptr();
   }
-  done(lse_gemm_bf16_skinny(a.data_ptr(), w.data_ptr(), b, out.data_ptr(), dtype_code(out, "out"),
-                            atomic_add ? 1 : 0, (int)a.size(0), (int)w.size(0), (int)a.size(1),
-                            error_flag(), stream()),
+  TORCH_CHECK(out.scalar_type() == torch::kInt64, "gemm_bf16_skinny: out must be int64 (fixed-point sums)");
+  done(lse_gemm_bf16_skinny(a.data_ptr(), w.data_ptr(), b, out.data_ptr(),
+                            (int)a.size(0), (int)w.size(0), (int)a.size(1), error_flag(), stream()),
        "gemm_bf16_skinny");
+}
+
+// out (+)= value of the fixed-point sums in acc; acc is left zero
+void fixed_to_float(Tensor& acc, Tensor& out, bool add) {
+  check_cuda(acc, "acc");
+  check_cuda(out, "out");
+  TORCH_CHECK(acc.scalar_type() == torch::kInt64 && acc.numel() == out.numel(),
+              "fixed_to_float: acc must be int64 with as many elements as out");
+  const int code = dtype_code(out, "out");
+  TORCH_CHECK(code != LSE_FIXED64 && (!add || code == LSE_F32), "fixed_to_float: bad out dtype");
+  done(lse_fixed_to_float(acc.data_ptr(), out.data_ptr(), code, add ? 1 : 0, (long long)acc.numel(), stream()),
+       "fixed_to_float");
 }
 
 // ------------------------------------------------------------------ attention libraries
@@ -452,6 +473,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_f32", &gemm_f32);
   m.def("gemm_bf16_skinny", &gemm_bf16_skinny);
   m.def("gemm_bf16_skinny_max_rows", &gemm_bf16_skinny_max_rows);
+  m.def("fixed_to_float", &fixed_to_float);
   m.def("kernel_error", &kernel_error);
   m.def("clear_kernel_error", &clear_kernel_error);
   m.def("load_attention_library", &load_attention_library);

@@ -12,6 +12,12 @@ namespace lse {
 
 typedef __nv_bfloat16 bf16;
 
+// Fixed-point sums (LSE_FIXED64 in kernels.h): value * 2^24 in a 64-bit integer.
+typedef long long fixed64;
+constexpr float kFixedScale = 16777216.f;
+constexpr float kFixedInverse = 1.f / 16777216.f;
+__device__ __forceinline__ float fixed_to_float(fixed64 v) { return (float)v * kFixedInverse; }
+
 template <typename T>
 struct Num;
 
@@ -27,6 +33,13 @@ struct Num<bf16> {
   static constexpr int kVec = 8;
   __device__ __forceinline__ static float to_float(bf16 v) { return __bfloat162float(v); }
   __device__ __forceinline__ static bf16 from_float(float v) { return __float2bfloat16_rn(v); }
+};
+
+template <>
+struct Num<fixed64> {
+  static constexpr int kVec = 2;
+  __device__ __forceinline__ static float to_float(fixed64 v) { return fixed_to_float(v); }
+  __device__ __forceinline__ static fixed64 from_float(float v) { return __float2ll_rn(v * kFixedScale); }
 };
 
 // 16-byte vector of T, read and written as one transaction.

@@ -1,19 +1,21 @@
 // bfloat16 matrix product for few rows (decode), on the 5th-generation tensor cores:
-//   out[T, N] (+)= a[T, K] . w[N, K]^T        T <= 256, float32 accumulation
+//   out[T, N] += a[T, K] . w[N, K]^T        T <= 32, float32 accumulation in the tensor cores
 //
 // With few rows the product is bound by streaming the weights once from HBM, so the operands are
 // swapped: the *weights* are the 128-row operand of tcgen05.mma (M = 128 output features per
-// block) and the tokens are its N dimension (16..256). Both operands are K-major in global memory
+// block) and the tokens are its N dimension (16 or 32). Both operands are K-major in global memory
 // already, so TMA brings [rows, 64] tiles straight into 128-byte-swizzled shared memory. One
 // elected thread issues tcgen05.mma (cta_group::1, kind::f16) with the accumulator [128 x T] in
 // tensor memory; another thread runs the TMA pipeline; all four warps read the accumulator back
 // with tcgen05.ld and write out[t, n] with n across lanes (coalesced).
 //
-// The kernel is persistent: one block per SM walks a contiguous range of (tile, k stage) units. With
-// atomic_add the ranges are balanced over all blocks whatever N is (a tile's K may be shared by
-// several blocks) and partial sums are added with float32 atomics into `out`, which the caller
-// has zeroed or which already holds the residual stream. Without it every block runs whole tiles
-// and stores them.
+// The kernel is persistent: blocks walk contiguous ranges of (tile, k stage) units, balanced over
+// all blocks whatever N is, so a tile's K may be shared by several blocks. The output is a buffer
+// of 64-bit fixed-point numbers (LSE_FIXED64) to which every block *adds* its partial sums with
+// integer atomics: value * 2^24, rounded to an integer. Integer addition is associative, so the
+// order in which the blocks arrive does not matter: the same inputs give the same bits on every
+// run, and a row's sum does not depend on the other rows of the batch (a float32 atomic sum would
+// depend on the order). The kernel that consumes the buffer converts back and clears it.
 //
 // Every wait on an mbarrier is bounded: on expiry the block records an error code in *error_flag
 // and leaves through the normal teardown (tensor memory is released).
@@ -41,10 +43,7 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, ui
 struct Params {
   int T, N, K;
   int tiles, chunks;      // output tiles of 128 features; k stages of 64 per tile
-  int whole_tiles;        // 1: every block runs whole tiles (plain stores); 0: balanced k ranges
-  int out_dtype;          // LSE_F32 or LSE_BF16
-  int atomic_add;         // add into out with float32 atomics (out float32)
-  void* out;
+  unsigned long long* out;  // [T, N] fixed-point sums
   const bf16* bias;       // [N] or nullptr (added with the first k stage of a tile)
   int* error_flag;
 };
@@ -52,23 +51,17 @@ struct Params {
 // Work of one block: units [u_begin, u_end) of the sequence (tile 0 stage 0, tile 0 stage 1, ...).
 __device__ __forceinline__ void block_range(const Params& p, long long& u_begin, long long& u_end) {
   const long long G = gridDim.x, g = blockIdx.x;
-  if (p.whole_tiles) {
-    u_begin = (g * p.tiles / G) * p.chunks;
-    u_end = ((g + 1) * p.tiles / G) * p.chunks;
-  } else {
-    const long long U = (long long)p.tiles * p.chunks;
-    u_begin = g * U / G;
-    u_end = (g + 1) * U / G;
-  }
+  const long long U = (long long)p.tiles * p.chunks;
+  u_begin = g * U / G;
+  u_end = (g + 1) * U / G;
 }
 
 // Persistent, warp-specialised kernel. 192 threads: warp 0 runs the TMA pipeline, warp 1 issues the
 // MMAs, warps 2..5 read accumulators back and write the output. A block walks a contiguous range
 // of (tile, k stage) units; each maximal run of units of one tile is a *segment* with its own
 // accumulator in tensor memory. Two accumulators alternate, so the epilogue of one segment overlaps
-// the loads and MMAs of the next. A segment that covers all of K is stored; a partial one is added
-// to the output with float32 atomics.
-// NT: tokens per block, padded (MMA N): 16, 32, 64, 128 or 256. STAGES: pipeline depth.
+// the loads and MMAs of the next.
+// NT: tokens per block, padded (MMA N): 16 or 32. STAGES: pipeline depth.
 template <int NT, int STAGES>
 __global__ void __launch_bounds__(192)
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
@@ -94,8 +87,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   long long u_begin, u_end;
   block_range(p, u_begin, u_end);
   const int my_units = (int)(u_end - u_begin);
-
-  pdl_trigger();
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -121,6 +112,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // Dependents may become resident only now that this block holds its tensor memory: one that
+  // allocated columns first and then sat in its dependency wait could block this allocation.
+  pdl_trigger();
 
   // Lanes 1..31 of the two role warps wait at __syncwarp, not on a barrier: a lane that spins in
   // try_wait would take turns with the role lane of its own warp and stall the pipeline.
@@ -210,7 +204,6 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool whole = seg_units == p.chunks;
       const int n = tile * BM + quarter * 32 + lane;
       const float bias = (p.bias && kc0 == 0 && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
 #pragma unroll 1
@@ -232,10 +225,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (t >= p.T) break;
             const float val = __uint_as_float(v[j]) + bias;
             const size_t o = (size_t)t * p.N + n;
-            if (p.atomic_add) atomicAdd(reinterpret_cast<float*>(p.out) + o, val);
-            else if (!whole) failed = 5;  // a partial sum cannot be stored without atomics
-            else if (p.out_dtype == LSE_F32) reinterpret_cast<float*>(p.out)[o] = val;
-            else reinterpret_cast<bf16*>(p.out)[o] = __float2bfloat16_rn(val);
+            atomicAdd(p.out + o, (unsigned long long)__float2ll_rn(val * kFixedScale));
           }
         }
       }
@@ -296,36 +286,26 @@ static int sm_count() {
 
 using namespace lse;
 
-extern "C" int lse_gemm_bf16_skinny_max_rows(void) { return 256; }
+extern "C" int lse_gemm_bf16_skinny_max_rows(void) { return 32; }
 
 extern "C" int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out,
-                                    int out_dtype, int atomic_add, int T, int N, int K,
-                                    int* error_flag, cudaStream_t stream) {
+                                    int T, int N, int K, int* error_flag, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return LSE_OK;
-  if (T > 256 || K <= 0 || K % 8) return LSE_BAD_ARGUMENT;
+  if (T > 32 || K <= 0 || K % 8) return LSE_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) return LSE_BAD_ARGUMENT;
-  if (atomic_add && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
-  const int nt = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (!out || (reinterpret_cast<uintptr_t>(out) & 7)) return LSE_BAD_ARGUMENT;
+  const int nt = T <= 16 ? 16 : 32;
   CUtensorMap mw, ma;
   if (!tma::make_map_bf16(&mw, w, N, K, K, tc::BM) || !tma::make_map_bf16(&ma, a, T, K, K, nt)) return LSE_LAUNCH_FAILED;
   tc::Params p;
   p.T = T; p.N = N; p.K = K;
   p.tiles = (N + tc::BM - 1) / tc::BM;
   p.chunks = (K + tc::BK - 1) / tc::BK;
-  p.whole_tiles = atomic_add ? 0 : 1;
-  p.out_dtype = out_dtype; p.atomic_add = atomic_add; p.out = out;
+  p.out = reinterpret_cast<unsigned long long*>(out);
   p.bias = reinterpret_cast<const bf16*>(bias); p.error_flag = error_flag;
   const long long units = (long long)p.tiles * p.chunks;
   // two blocks per SM (five stages each fit twice in shared memory) keep more copies in flight
-  const int per_sm = nt <= 64 ? 2 : 1;
-  int grid = tc::sm_count() * per_sm;
-  if (p.whole_tiles) grid = grid < p.tiles ? grid : p.tiles;
-  else if (units < grid) grid = (int)units;
-  switch (nt) {
-    case 16: return tc::launch<16, 5>(mw, ma, p, grid, stream);
-    case 32: return tc::launch<32, 5>(mw, ma, p, grid, stream);
-    case 64: return tc::launch<64, 4>(mw, ma, p, grid, stream);
-    case 128: return tc::launch<128, 6>(mw, ma, p, grid, stream);
-    default: return tc::launch<256, 4>(mw, ma, p, grid, stream);
-  }
+  int grid = tc::sm_count() * 2;
+  if (units < grid) grid = (int)units;
+  return nt == 16 ? tc::launch<16, 5>(mw, ma, p, grid, stream) : tc::launch<32, 5>(mw, ma, p, grid, stream);
 }

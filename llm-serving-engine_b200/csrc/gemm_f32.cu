@@ -89,5 +89,5 @@ extern "C" int lse_gemm_f32(const float* a, const float* w, const float* bias, f
   dim3 grid((N + lse::BN - 1) / lse::BN, (T + lse::BM - 1) / lse::BM);
   if (grid.y > 65535) return LSE_BAD_ARGUMENT;
   lse::gemm_f32_kernel<<<grid, 256, 0, stream>>>(a, w, bias, out, T, N, K);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }

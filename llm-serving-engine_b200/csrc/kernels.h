@@ -4,12 +4,17 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #include "status.h"
 
 #define LSE_F32 0
 #define LSE_BF16 1
+// Sums that several blocks add to in any order: a 64-bit integer holding value * 2^24. Integer
+// addition is associative, so the result has the same bits whatever the order was. A kernel that
+// takes such an input converts it to float32 and leaves zeros behind, ready for the next sums.
+#define LSE_FIXED64 2
 
 extern "C" {
 
@@ -21,6 +26,8 @@ int lse_embedding(const int* ids, const void* table, int table_dtype, float* out
 //   rows == nullptr: for every row t < T: if residual: x[t] += residual[t] (in place, float32);
 //                    out[t] = x[t] * rsqrt(mean(x[t]^2) + eps) * weight
 //   rows != nullptr: out[r] = norm(x[rows[r]] (+ residual[rows[r]])) for r < T; x is not written.
+// residual_dtype LSE_FIXED64 (rows == nullptr only): residual holds fixed-point sums, which are
+// cleared as they are read.
 int lse_add_rmsnorm(float* x, const void* residual, int residual_dtype, const float* weight,
                     float eps, void* out, int out_dtype, const int* rows, int T, int H,
                     cudaStream_t stream);
@@ -28,19 +35,19 @@ int lse_add_rmsnorm(float* x, const void* residual, int residual_dtype, const fl
 // Rotate the q and k heads of the fused projection and write this step's k and v rows into their
 // pages. qkv [T, (nq + 2 nk) D] of in_dtype; the rotated queries go to q_out as `dtype`:
 //   in_dtype == dtype: q_out must be qkv itself (rotated in place, row stride (nq + 2 nk) D);
-//   in_dtype == LSE_F32, dtype == LSE_BF16: q_out is a separate [T, nq D] buffer.
+//   in_dtype == LSE_F32 or LSE_FIXED64 (cleared as it is read), dtype == LSE_BF16: q_out is a
+//   separate [T, nq D] buffer.
 //   cos/sin float32 [max_pos, D/2] or nullptr for no rotation;
 //   k_pages/v_pages [pages, nk, page_tokens, D] of `dtype`, or nullptr when this layer only reads.
 int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int dtype, int T, int nq, int nk,
                       int D, const int* positions, const int* token_seq, const float* cos,
                       const float* sin, void* k_pages, void* v_pages, const int* block_tables,
-                      int table_stride, int page_tokens, int zero_in, cudaStream_t stream);
+                      int table_stride, int page_tokens, cudaStream_t stream);
 
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i]     gu [T, 2I] of in_dtype, out [T, I] of dtype
-// (in_dtype == dtype, or float32 in and bfloat16 out). zero_in = 1 (float32 in, bfloat16 out
-// only; also for lse_rope_kv_write): the input is an accumulation buffer of the few-rows matrix
-// product; every element that is read is set to zero, so the buffer is ready for the next product.
-int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I, int zero_in,
+// (in_dtype == dtype, or float32 / LSE_FIXED64 in and bfloat16 out; a fixed-point input is cleared
+// as it is read).
+int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I,
                  cudaStream_t stream);
 
 // True float32 matrix product: out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]). Each output element is
@@ -49,13 +56,18 @@ int lse_gemm_f32(const float* a, const float* w, const float* bias, float* out, 
                  cudaStream_t stream);
 
 // bfloat16 product for few rows on tcgen05 tensor cores fed by TMA (gemm_bf16_tc.cu):
-//   out[T, N] = a[T, K] . w[N, K]^T (+ bias[N]),  T <= lse_gemm_bf16_skinny_max_rows(), K % 8 == 0.
-// out_dtype LSE_F32 or LSE_BF16. With atomic_add = 1 (out float32) results are added to what out
-// holds and the work is balanced over all SMs whatever N is. error_flag (device-visible int, may be null)
-// receives a non-zero code if a bounded wait inside the kernel ran out.
+//   out[T, N] += a[T, K] . w[N, K]^T (+ bias[N]),  T <= lse_gemm_bf16_skinny_max_rows(), K % 8 == 0.
+// out is a buffer of 64-bit fixed-point numbers (see LSE_FIXED64). The work is balanced over all
+// SMs whatever N is; the sums do not depend on the order of the additions, so they have the same
+// bits on every run. error_flag (device-visible int, may be null) receives a non-zero code if a
+// bounded wait inside the kernel ran out.
 int lse_gemm_bf16_skinny_max_rows(void);
-int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out, int out_dtype,
-                         int atomic_add, int T, int N, int K, int* error_flag, cudaStream_t stream);
+int lse_gemm_bf16_skinny(const void* a, const void* w, const void* bias, void* out, int T, int N,
+                         int K, int* error_flag, cudaStream_t stream);
+
+// out[T, N] = value of the fixed-point sums acc[T, N] (+ what out holds, if add != 0); every
+// element of acc that is read is set to zero. out float32 or bfloat16 (add needs float32).
+int lse_fixed_to_float(void* acc, void* out, int out_dtype, int add, long long n, cudaStream_t stream);
 
 // Sampling. One token per row of logits [R, V] (float32, row stride V).
 //   temperature[r] < 1e-5 selects the largest logit (lowest index on ties). Otherwise the row is

@@ -52,6 +52,16 @@ __device__ __forceinline__ void load4<bf16>(const bf16* p, float (&v)[4]) {
   const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
   v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
 }
+// Fixed-point sums are taken: read, converted, and zeros left behind for the next sums.
+template <>
+__device__ __forceinline__ void load4<fixed64>(const fixed64* p, float (&v)[4]) {
+  longlong2* q = reinterpret_cast<longlong2*>(const_cast<fixed64*>(p));
+  const longlong2 a = q[0], b = q[1];
+  q[0] = make_longlong2(0, 0);
+  q[1] = make_longlong2(0, 0);
+  v[0] = fixed_to_float(a.x); v[1] = fixed_to_float(a.y);
+  v[2] = fixed_to_float(b.x); v[3] = fixed_to_float(b.y);
+}
 template <typename T>
 __device__ __forceinline__ void store4(T* p, const float (&v)[4]);
 template <>
@@ -291,7 +301,7 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
                                          const float* __restrict__ sin_t, T* __restrict__ k_pages,
                                          T* __restrict__ v_pages,
                                          const int* __restrict__ block_tables, int table_stride,
-                                         int page_tokens, int page_shift, int zero_in) {
+                                         int page_tokens, int page_shift) {
   // elements per item and half: a 16-byte vector when both sides are bfloat16 (D is a multiple of
   // 16 there, so a half holds whole vectors), four otherwise
   constexpr int V = (std::is_same<TIn, bf16>::value && std::is_same<T, bf16>::value) ? 8 : 4;
@@ -311,19 +321,15 @@ __global__ void rope_kv_write_vec_kernel(const TIn* qkv, T* q_out,
   }
   const float* c = cos_t ? cos_t + (size_t)pos * half : nullptr;
   const float* s = sin_t ? sin_t + (size_t)pos * half : nullptr;
-  // zero_in: the input is a float32 accumulation buffer that must read as zero afterwards
-  const int n_items = ((nq + nk) + ((k_pages || zero_in) ? nk : 0)) * chunks;
+  // fixed-point sums are cleared by reading them, so the value heads are visited even when this
+  // layer writes no pages
+  const int n_items = ((nq + nk) + ((k_pages || std::is_same<TIn, fixed64>::value) ? nk : 0)) * chunks;
   for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < n_items; it += gridDim.y * blockDim.x) {
     const int head = it / chunks, i = (it - head * chunks) * V;
     const TIn* h = row + (size_t)head * D;
     float a[V], b[V];
     loadv<TIn, V>(h + i, a);
     loadv<TIn, V>(h + i + half, b);
-    if (!std::is_same<TIn, T>::value && zero_in) {
-      const float z[V] = {};
-      storev<TIn, V>(const_cast<TIn*>(h) + i, z);
-      storev<TIn, V>(const_cast<TIn*>(h) + i + half, z);
-    }
     if (head < nq + nk && c) {
       float cv[V], sv[V];
       loadv<float, V>(c + i, cv);
@@ -359,7 +365,7 @@ __device__ __forceinline__ float silu_times(float a, float u) {
   else return a / (1.f + expf(-a)) * u;
 }
 template <typename TIn, typename T>
-__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I, int zero_in) {
+__global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out, int I) {
   pdl_trigger();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -371,11 +377,6 @@ __global__ void silu_mul_kernel(const TIn* __restrict__ gu, T* __restrict__ out,
       float gv[4], uv[4];
       load4<TIn>(g + i, gv);
       load4<TIn>(u + i, uv);
-      if (!std::is_same<TIn, T>::value && zero_in) {  // accumulation buffer: leave zeros behind
-        const float z[4] = {0.f, 0.f, 0.f, 0.f};
-        store4<TIn>(const_cast<TIn*>(g) + i, z);
-        store4<TIn>(const_cast<TIn*>(u) + i, z);
-      }
 #pragma unroll
       for (int j = 0; j < 4; ++j) gv[j] = silu_times<T>(gv[j], uv[j]);
       store4<T>(o + i, gv);
@@ -409,6 +410,32 @@ __global__ void silu_mul_wide_kernel(const T* __restrict__ gu, T* __restrict__ o
   store16(out + (size_t)t * I + (size_t)c * V, o);
 }
 
+// ------------------------------------------------------------------------------------ fixed-point sums
+// out[i] (+)= value of acc[i]; acc[i] = 0. VEC4: four elements per thread (n a multiple of 4).
+template <typename T, bool VEC4>
+__global__ void fixed_to_float_kernel(fixed64* __restrict__ acc, T* __restrict__ out, int add, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (VEC4 ? 4 : 1);
+  if (i >= n) return;
+  if (VEC4) {
+    float v[4];
+    load4<fixed64>(acc + i, v);  // clears what it reads
+    if (add) {
+      float o[4];
+      load4<T>(out + i, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] += o[j];
+    }
+    store4<T>(out + i, v);
+  } else {
+    float v = fixed_to_float(acc[i]);
+    acc[i] = 0;
+    if (add) v += Num<T>::to_float(out[i]);
+    out[i] = Num<T>::from_float(v);
+  }
+}
+
 static int shift_of(int n) {
   if (n <= 0 || (n & (n - 1))) return -1;
   int s = 0;
@@ -420,7 +447,7 @@ static int shift_of(int n) {
 
 using namespace lse;
 
-#define LSE_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED)
+#define LSE_CHECK_LAUNCH() (cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED)
 
 extern "C" int lse_embedding(const int* ids, const void* table, int table_dtype, float* out, int T,
                              int H, cudaStream_t stream) {
@@ -460,6 +487,16 @@ extern "C" int lse_add_rmsnorm(float* x, const void* residual, int residual_dtyp
   else if (residual_dtype == LSE_F32 && out_dtype == LSE_BF16) LSE_NORM(float, bf16);
   else if (residual_dtype == LSE_BF16 && out_dtype == LSE_BF16) LSE_NORM(bf16, bf16);
   else if (residual_dtype == LSE_BF16 && out_dtype == LSE_F32) LSE_NORM(bf16, float);
+  else if (residual_dtype == LSE_FIXED64 && out_dtype == LSE_BF16) {
+    // sums that are cleared as they are read: every row once, four elements at a time
+    if (!residual || rows || H % 4) return LSE_BAD_ARGUMENT;
+    if (regs)
+      launch(add_rmsnorm_regs_kernel<fixed64, bf16, 4>, T, threads, 0, stream, x,
+             (const fixed64*)residual, weight, eps, (bf16*)out, rows, H);
+    else
+      launch(add_rmsnorm_kernel<fixed64, bf16, true>, T, threads, 0, stream, x,
+             (const fixed64*)residual, weight, eps, (bf16*)out, rows, H);
+  }
   else return LSE_BAD_ARGUMENT;
 #undef LSE_NORM
   return LSE_CHECK_LAUNCH();
@@ -469,13 +506,13 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
                                  int nk, int D, const int* positions, const int* token_seq,
                                  const float* cos, const float* sin, void* k_pages, void* v_pages,
                                  const int* block_tables, int table_stride, int page_tokens,
-                                 int zero_in, cudaStream_t stream) {
+                                 cudaStream_t stream) {
   if (T <= 0) return LSE_OK;
-  if (zero_in && !(in_dtype == LSE_F32 && dtype == LSE_BF16 && (D / 2) % 4 == 0)) return LSE_BAD_ARGUMENT;
   if (D % 2 || page_tokens <= 0 || (cos == nullptr) != (sin == nullptr) ||
       (k_pages == nullptr) != (v_pages == nullptr))
     return LSE_BAD_ARGUMENT;
-  if (in_dtype != dtype && in_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
+  if (in_dtype != dtype && in_dtype != LSE_F32 && in_dtype != LSE_FIXED64) return LSE_BAD_ARGUMENT;
+  if (in_dtype == LSE_FIXED64 && (dtype != LSE_BF16 || (D / 2) % 4)) return LSE_BAD_ARGUMENT;
   if (in_dtype == dtype && q_out != qkv) return LSE_BAD_ARGUMENT;  // same type: rotated in place
   const int ps = shift_of(page_tokens);
   const bool wide = in_dtype == LSE_BF16 && dtype == LSE_BF16 && (D / 2) % 8 == 0;  // the kernel's V = 8
@@ -483,13 +520,14 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
 #define LSE_ROPE_VEC(TIn, T)                                                                      \
   launch(rope_kv_write_vec_kernel<TIn, T>, vgrid, 128, 0, stream,                                 \
          (const TIn*)qkv, (T*)q_out, nq, nk, D, positions, token_seq, cos, sin, (T*)k_pages,      \
-         (T*)v_pages, block_tables, table_stride, page_tokens, ps, zero_in)
+         (T*)v_pages, block_tables, table_stride, page_tokens, ps)
   // one thread per item (head, chunk of V + V elements): every load of a token is in flight at once
   const int items = (nq + 2 * nk) * (D / (wide ? 16 : 8));
   const dim3 vgrid(T, (items + 127) / 128 > 64 ? 64 : (items + 127) / 128);
   if (vec && in_dtype == LSE_F32 && dtype == LSE_F32) LSE_ROPE_VEC(float, float);
   else if (vec && in_dtype == LSE_BF16 && dtype == LSE_BF16) LSE_ROPE_VEC(bf16, bf16);
   else if (vec && in_dtype == LSE_F32 && dtype == LSE_BF16) LSE_ROPE_VEC(float, bf16);
+  else if (in_dtype == LSE_FIXED64) LSE_ROPE_VEC(fixed64, bf16);
   else if (in_dtype != dtype) return LSE_BAD_ARGUMENT;
   else if (dtype == LSE_F32)
     rope_kv_write_kernel<float><<<T, 256, 0, stream>>>(
@@ -506,9 +544,8 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, void* q_out, int
 }
 
 extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, int T, int I,
-                            int zero_in, cudaStream_t stream) {
+                            cudaStream_t stream) {
   if (T <= 0 || I <= 0) return LSE_OK;
-  if (zero_in && !(in_dtype == LSE_F32 && dtype == LSE_BF16 && I % 4 == 0)) return LSE_BAD_ARGUMENT;
   const int threads = 256;
   const int vec = in_dtype == LSE_BF16 ? 8 : 4;
   if (in_dtype == dtype && I % vec == 0 && (size_t)T * (I / vec) < (1ull << 31) &&
@@ -524,12 +561,39 @@ extern "C" int lse_silu_mul(const void* gu, int in_dtype, void* out, int dtype, 
   const int per_block = threads * 4;
   dim3 grid(T, min((I + per_block - 1) / per_block, 65535));
   if (in_dtype == LSE_F32 && dtype == LSE_F32)
-    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I, 0);
+    launch(silu_mul_kernel<float, float>, grid, threads, 0, stream, (const float*)gu, (float*)out, I);
   else if (in_dtype == LSE_BF16 && dtype == LSE_BF16)
-    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I, 0);
+    launch(silu_mul_kernel<bf16, bf16>, grid, threads, 0, stream, (const bf16*)gu, (bf16*)out, I);
   else if (in_dtype == LSE_F32 && dtype == LSE_BF16)
-    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I, zero_in);
+    launch(silu_mul_kernel<float, bf16>, grid, threads, 0, stream, (const float*)gu, (bf16*)out, I);
+  else if (in_dtype == LSE_FIXED64 && dtype == LSE_BF16 && I % 4 == 0)
+    launch(silu_mul_kernel<fixed64, bf16>, grid, threads, 0, stream, (const fixed64*)gu, (bf16*)out, I);
   else
     return LSE_BAD_ARGUMENT;
+  return LSE_CHECK_LAUNCH();
+}
+
+extern "C" int lse_fixed_to_float(void* acc, void* out, int out_dtype, int add, long long n,
+                                  cudaStream_t stream) {
+  if (n <= 0) return LSE_OK;
+  if (add && out_dtype != LSE_F32) return LSE_BAD_ARGUMENT;
+  const int threads = 128;
+  const bool vec = n % 4 == 0 && reinterpret_cast<uintptr_t>(acc) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  const long long items = vec ? n / 4 : n;
+  const long long blocks = (items + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return LSE_BAD_ARGUMENT;
+#define LSE_CONVERT(T, V) \
+  launch(fixed_to_float_kernel<T, V>, (unsigned)blocks, threads, 0, stream, (fixed64*)acc, (T*)out, add, n)
+  if (out_dtype == LSE_F32) {
+    if (vec) LSE_CONVERT(float, true);
+    else LSE_CONVERT(float, false);
+  } else if (out_dtype == LSE_BF16) {
+    if (vec) LSE_CONVERT(bf16, true);
+    else LSE_CONVERT(bf16, false);
+  } else {
+    return LSE_BAD_ARGUMENT;
+  }
+#undef LSE_CONVERT
   return LSE_CHECK_LAUNCH();
 }

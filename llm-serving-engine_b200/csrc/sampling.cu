@@ -657,7 +657,7 @@ extern "C" int lse_sample(const float* logits, int R, int V, const float* temper
   if (parallel && (which & 2))
     launch(sample_parallel_kernel, dim3(R, SAMPLE_CHUNKS), PAR_THREADS, 0, stream, logits, V, temperature,
            top_k, top_p, min_p, seed, draw, out_tokens, scratch, scratch_rows);
-  if (parallel && !(which & 1)) return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  if (parallel && !(which & 1)) return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
   // histogram / candidate list, and the row itself when it fits beside them
   const size_t base = (size_t)HIST_BINS * 12;
   const size_t cached = base + (size_t)V * 4;
@@ -677,13 +677,13 @@ extern "C" int lse_sample(const float* logits, int R, int V, const float* temper
   else
     launch(sample_kernel<false>, R, SAMPLE_THREADS, base, stream, logits, V, temperature, top_k, top_p,
            min_p, seed, draw, out_tokens, (parallel && (which & 2)) ? 1 : 0);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 extern "C" int lse_logsumexp(const float* logits, int R, int V, float* out, cudaStream_t stream) {
   if (R <= 0) return LSE_OK;
   logsumexp_kernel<<<R, 512, 0, stream>>>(logits, V, out);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 extern "C" int lse_apply_penalties(float* logits, int V, const int* row, const int* token,
@@ -692,21 +692,21 @@ extern "C" int lse_apply_penalties(float* logits, int V, const int* row, const i
   if (n <= 0) return LSE_OK;
   penalties_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, V, row, token, count, presence,
                                                         frequency, repetition, n);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 extern "C" int lse_ban_tokens(float* logits, int V, const int* row, const int* token, int n,
                               cudaStream_t stream) {
   if (n <= 0) return LSE_OK;
   ban_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, V, row, token, n);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 extern "C" int lse_token_state_add(int* state, int V, const int* slot, const int* token,
                                    const int* in_prompt, int n, cudaStream_t stream) {
   if (n <= 0) return LSE_OK;
   token_state_add_kernel<<<(n + 255) / 256, 256, 0, stream>>>(state, V, slot, token, in_prompt, n);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }
 
 extern "C" int lse_apply_penalties_dense(float* logits, int V, const int* row, const int* slot,
@@ -717,5 +717,5 @@ extern "C" int lse_apply_penalties_dense(float* logits, int V, const int* row, c
   if (n > 65535) return LSE_BAD_ARGUMENT;
   penalties_dense_kernel<<<dim3((V + 255) / 256, n), 256, 0, stream>>>(logits, V, row, slot, presence,
                                                                        frequency, repetition, state);
-  return cudaGetLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+  return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
 }

@@ -30,6 +30,7 @@ mechanism differs.
 
 from __future__ import annotations
 
+import gc
 from typing import Sequence
 
 import numpy as np
@@ -525,12 +526,21 @@ class DecodeGraphs:
         g.graph = torch.cuda.CUDAGraph()
         if self.pool is None:
             self.pool = torch.cuda.graph_pool_handle()
-        with torch.cuda.stream(side):
-            g.graph.capture_begin(pool=self.pool)
-            try:
-                out = self._forward(g)
-            finally:
-                g.graph.capture_end()
+        # No cyclic garbage collection while the stream captures: an engine of earlier use that
+        # is collected just then destroys its graphs, which is not permitted during a capture and
+        # would invalidate this one.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.stream(side):
+                g.graph.capture_begin(pool=self.pool)
+                try:
+                    out = self._forward(g)
+                finally:
+                    g.graph.capture_end()
+        finally:
+            if collecting:
+                gc.enable()
         cur.wait_stream(side)
         if g.sampled:
             g.tokens = out

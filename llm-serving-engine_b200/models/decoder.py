@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from ..parts.base import BLOCKS, NORMS, POSITION_ENCODINGS, BuildEnv, ParamDecl, role_dtype
+from ..parts.base import BLOCKS, NORMS, POSITION_ENCODINGS, BuildEnv, ParamDecl, role_dtype, settle
 from .plan import ModelPlan
 
 
@@ -108,6 +108,8 @@ class DecoderModel:
             view = pools.view(e.cache, writes=self.writer_of[e.cache] == k)
             x, pending = self.blocks[e.layer].forward(x, pending, step, view)
         if step.num_logit_rows == 0:
+            if hasattr(pending, "resolve"):
+                pending.resolve()  # nobody reads x any more, but the kernel set's sums must be taken
             return torch.empty(0, self.plan.vocab_size, dtype=torch.float32, device=x.device)
-        h = self.final_norm.forward(x, pending, rows=step.logit_rows)
+        h = self.final_norm.forward(x, settle(pending, self.final_norm), rows=step.logit_rows)
         return self.ops.linear(h, self.head_weight, None, out_dtype=torch.float32)

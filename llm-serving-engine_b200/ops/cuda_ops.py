@@ -4,8 +4,17 @@ There is no other implementation behind these methods: if CUDA or the compiled e
 available, constructing :class:`CudaOps` raises.
 
 Matrix products: float32 runs this package's own CUDA-core kernel (true 32-bit, no tensor-core
-mode). bfloat16 products go to cuBLAS through ``torch.mm`` with float32 accumulation, the same
+mode). bfloat16 products of up to 32 rows (decoding) run this package's tcgen05 kernel; with more
+rows they go to cuBLAS through ``torch.mm`` with float32 accumulation, the same
 library-for-linear-layers split as the reference (src/llmserve/models/layers.py:129-152).
+
+The few-rows kernel shares a tile's K between blocks, which add their partial sums with integer
+atomics into a buffer of 64-bit fixed-point numbers (value * 2^24). Such sums have the same bits
+whatever the order of the additions was, so the bfloat16 path is reproducible from run to run.
+The kernel that consumes the product (rotation and cache write, SiLU, residual add and norm, or a
+plain conversion) reads the buffer, converts and leaves zeros behind. The buffers never leave
+this class except as a :class:`PendingSums` that stands for "a product still to be added to the
+residual stream".
 """
 
 from __future__ import annotations
@@ -18,8 +27,34 @@ from . import build
 _DTYPES = (torch.float32, torch.bfloat16)
 
 
+class PendingSums:
+    """A product that is still to be added to the float32 tensor ``into`` (the residual stream).
+
+    What a projection called with ``accumulate_into=x, may_defer=True`` may return instead of
+    adding at once: the sums lie in a fixed-point buffer of the kernel set. Hand it, as the
+    ``residual``, to the next ``add_rmsnorm`` on the same ``x`` (which adds it while it reads it
+    anyway), or call :meth:`resolve` to have it added now. Exactly one of the two must happen
+    before anything else reads ``x``.
+    """
+
+    __slots__ = ("ops", "sums", "into")
+
+    def __init__(self, ops: "CudaOps", sums: torch.Tensor, into: torch.Tensor) -> None:
+        self.ops, self.sums, self.into = ops, sums, into
+
+    def resolve(self) -> None:
+        """Add the sums to ``into`` now. Returns None: nothing is pending any more."""
+        if self.sums is not None:
+            self.ops.ext.fixed_to_float(self.sums, self.into, True)
+            self.ops.launches += 1
+            self.ops._sums_taken(self.sums)
+            self.sums = None
+        return None
+
+
 class CudaOps:
     name = "cuda-sm100a"
+    defers_adds = True  # linear(..., accumulate_into=x, may_defer=True) may return PendingSums
 
     def __init__(self, device: torch.device | str = "cuda") -> None:
         self.device = torch.device(device)
@@ -35,13 +70,13 @@ class CudaOps:
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.attention_kernel = 0  # 0: fastest available; 1: CUDA cores; 2: mma.sync (tests compare them)
         self.use_skinny_gemm = True
+        # rows up to which the own tcgen05 product runs (measured: above it the library is faster)
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())
-        self.skinny_atomic_rows = 32  # measured: above this the library's kernels are faster
-        # float32 accumulation buffers of the few-rows product, by shape. Invariant: a buffer that
-        # is not in _ws_live reads as zero (the kernel that consumes a product zeroes what it reads).
+        # Fixed-point sum buffers of the few-rows product, by shape. A buffer is zero whenever it
+        # is not in _sums_live (the kernel that takes a product's sums leaves zeros behind).
+        self._sums: dict[tuple[int, int], torch.Tensor] = {}
+        self._sums_live: set[int] = set()  # data_ptr of buffers whose sums have not been taken yet
         self._addmm_in_place: bool | None = None  # whether torch.addmm can add into a float32 tensor
-        self._ws: dict[tuple[int, int], torch.Tensor] = {}
-        self._ws_live: dict[int, tuple[int, int]] = {}  # data_ptr -> shape of products not yet consumed
         self.launches = 0  # kernels of this package enqueued (library matrix products not counted)
 
     # ------------------------------------------------------------------ capabilities
@@ -81,57 +116,62 @@ class CudaOps:
         return out
 
     def add_rmsnorm(self, x, residual, weight, eps, out_dtype, rows=None):
+        """``residual`` may be a :class:`PendingSums` for ``x``: its sums are added as they are read."""
+        sums = None
+        if isinstance(residual, PendingSums):
+            if residual.into is not x:
+                raise ValueError("these pending sums belong to another tensor")
+            if rows is None and out_dtype == torch.bfloat16 and x.shape[1] % 4 == 0 and residual.sums is not None:
+                sums, residual.sums = residual.sums, None
+                residual = sums
+            else:  # only some rows are read here, so the whole product is added first
+                residual = residual.resolve()
         n = x.shape[0] if rows is None else rows.shape[0]
         out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
         self.ext.add_rmsnorm(x, residual, weight, float(eps), out, rows)
         self.launches += 1
+        if sums is not None:
+            self._sums_taken(sums)
         return out
 
-    def _accumulator(self, T: int, N: int) -> torch.Tensor:
-        """A zero float32 ``[T, N]`` buffer for atomic sums: the persistent one of this shape if its
-        last product has been consumed, else a fresh one."""
-        ws = self._ws.get((T, N))
-        if ws is None and not torch.cuda.is_current_stream_capturing():
-            ws = self._ws[(T, N)] = torch.zeros(T, N, dtype=torch.float32, device=self.device)
-        if ws is None or ws.data_ptr() in self._ws_live:
-            return torch.zeros(T, N, dtype=torch.float32, device=self.device)
-        self._ws_live[ws.data_ptr()] = (T, N)
-        return ws
+    # ------------------------------------------------------------------ fixed-point sums
+    def _product_sums(self, a, w, bias) -> torch.Tensor:
+        """``a @ w.T (+ bias)`` as fixed-point sums in a buffer that the caller must have taken
+        (by a kernel that clears it) before the buffer of this shape is used again."""
+        T, N = a.shape[0], w.shape[0]
+        buf = self._sums.get((T, N))
+        if buf is None and not torch.cuda.is_current_stream_capturing():
+            buf = self._sums[(T, N)] = torch.zeros(T, N, dtype=torch.int64, device=self.device)
+        if buf is None or buf.data_ptr() in self._sums_live:
+            buf = torch.zeros(T, N, dtype=torch.int64, device=self.device)  # rare: the shape's buffer is busy
+        self._sums_live.add(buf.data_ptr())
+        self.ext.gemm_bf16_skinny(a, w, bias, buf)
+        self.launches += 1
+        return buf
 
-    def _consumes(self, t: torch.Tensor, out_dtype, kernel_can_zero: bool) -> bool:
-        """True if ``t`` is a live accumulation buffer that the consuming kernel will zero."""
-        if t.data_ptr() not in self._ws_live:
-            return False
-        if t.dtype == torch.float32 and out_dtype == torch.bfloat16 and kernel_can_zero:
-            del self._ws_live[t.data_ptr()]
-            return True
-        return False
-
-    def _release(self, t: torch.Tensor) -> None:
-        """``t`` was read by a kernel that did not zero it: restore the zero invariant."""
-        if self._ws_live.pop(t.data_ptr(), None) is not None:
-            t.zero_()
+    def _sums_taken(self, buf: torch.Tensor) -> None:
+        self._sums_live.discard(buf.data_ptr())
 
     def silu_mul(self, gu, out_dtype=None):
         out_dtype = out_dtype or gu.dtype
         out = torch.empty(gu.shape[0], gu.shape[1] // 2, dtype=out_dtype, device=gu.device)
-        zero = self._consumes(gu, out_dtype, gu.shape[1] % 8 == 0)
-        self.ext.silu_mul(gu, out, zero)
-        if not zero:
-            self._release(gu)
+        self.ext.silu_mul(gu, out)
         self.launches += 1
         return out
 
     # ------------------------------------------------------------------ matrix products
-    def linear(self, a, w, bias=None, out_dtype=None, accumulate_into=None):
-        """``a @ w.T (+ bias)``.
+    def _few_rows(self, a, w) -> bool:
+        """Does the own tcgen05 kernel serve this product?"""
+        return (self.use_skinny_gemm and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and a.shape[0] <= self.skinny_max_rows and a.shape[1] % 8 == 0)
 
-        out_dtype None asks for "an activation for the next kernel of this package": the compute
-        dtype, or float32 sums where those come for free (the kernels that read activations take
-        both; a float32 result may be an internal accumulation buffer that ``rope_kv_write`` or
-        ``silu_mul`` clears as it reads it, so it must not be read again after that).
+    def linear(self, a, w, bias=None, out_dtype=None, accumulate_into=None, may_defer=False):
+        """``a @ w.T (+ bias)`` as a new tensor of ``out_dtype`` (None: the compute dtype).
+
         With ``accumulate_into`` (a float32 tensor of the result's shape) the product may be
-        added into that tensor instead; the return value is then None.
+        added into that tensor instead; the return value is then None. A caller that passes
+        ``may_defer=True`` may get a :class:`PendingSums` instead, which it has to hand on to
+        whoever reads ``accumulate_into`` next.
         """
         if a.dtype == torch.float32:
             if w.dtype != torch.float32:
@@ -142,24 +182,19 @@ class CudaOps:
             return out if out_dtype in (None, torch.float32) else out.to(out_dtype)
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise TypeError(f"linear: unsupported dtypes {a.dtype} x {w.dtype}")
-        T, K = a.shape
+        T = a.shape[0]
         N = w.shape[0]
-        if self.use_skinny_gemm and T <= self.skinny_atomic_rows and K % 8 == 0:
+        if self._few_rows(a, w):
             # few rows: the weights are streamed once through the tcgen05 kernel, work balanced
-            # over all SMs, float32 sums added with atomics
-            if out_dtype == torch.bfloat16:
-                out = torch.empty(T, N, dtype=torch.bfloat16, device=a.device)
-                self.ext.gemm_bf16_skinny(a, w, bias, out, False)
-                self.launches += 1
-                return out
+            # over all SMs, partial sums added as fixed-point numbers
+            sums = self._product_sums(a, w, bias)
             if accumulate_into is not None:
-                self.ext.gemm_bf16_skinny(a, w, bias, accumulate_into, True)
-                self.launches += 1
-                return None
-            out = (self._accumulator(T, N) if out_dtype is None
-                   else torch.zeros(T, N, dtype=torch.float32, device=a.device))
-            self.ext.gemm_bf16_skinny(a, w, bias, out, True)
+                pending = PendingSums(self, sums, accumulate_into)
+                return pending if may_defer else pending.resolve()
+            out = torch.empty(T, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+            self.ext.fixed_to_float(sums, out, False)
             self.launches += 1
+            self._sums_taken(sums)
             return out
         if accumulate_into is not None and bias is None and self._addmm_in_place is not False:
             # many rows: the library adds the product into the residual stream (beta = 1)
@@ -180,16 +215,41 @@ class CudaOps:
             return torch.addmm(bias, a, w.t())  # bias added before the one rounding to bfloat16
         return torch.mm(a, w.t())
 
+    def gated_silu(self, h, w, bias=None, out_dtype=None):
+        """``silu(h @ gate.T) * (h @ up.T)`` for ``w = [gate rows; up rows]``. With few bfloat16
+        rows the gate meets its activation as a float32 value (the activation kernel takes the
+        product's fixed-point sums); otherwise as the product's rounded output."""
+        out_dtype = out_dtype or h.dtype
+        if self._few_rows(h, w) and out_dtype == torch.bfloat16 and w.shape[0] % 8 == 0:
+            sums = self._product_sums(h, w, bias)
+            out = self.silu_mul(sums, out_dtype=out_dtype)
+            self._sums_taken(sums)
+            return out
+        return self.silu_mul(self.linear(h, w, bias), out_dtype=out_dtype)
+
+    def project_rope_kv_write(self, h, w, bias, *, num_heads, num_kv_heads, head_dim, positions,
+                              token_seq, cos, sin, k_pages, v_pages, block_tables, page_tokens,
+                              out_dtype):
+        """The fused q|k|v projection of ``h``, rotation of q and k, and the write of k and v into
+        their pages; returns the rotated queries. With few bfloat16 rows q, k and v reach the
+        rotation as float32 values (the rotation kernel takes the product's fixed-point sums)."""
+        kw = dict(num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                  positions=positions, token_seq=token_seq, cos=cos, sin=sin, k_pages=k_pages,
+                  v_pages=v_pages, block_tables=block_tables, page_tokens=page_tokens, out_dtype=out_dtype)
+        if self._few_rows(h, w) and out_dtype == torch.bfloat16 and head_dim % 8 == 0:
+            sums = self._product_sums(h, w, bias)
+            q = self.rope_kv_write(sums, **kw)
+            self._sums_taken(sums)
+            return q
+        return self.rope_kv_write(self.linear(h, w, bias), **kw)
+
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
                       cos, sin, k_pages, v_pages, block_tables, page_tokens, out_dtype):
         """Rotate q and k, write k and v into their pages; returns the rotated queries."""
-        zero = self._consumes(qkv, out_dtype, head_dim % 8 == 0)
         q = self.ext.rope_kv_write(qkv, num_heads, num_kv_heads, head_dim, positions, token_seq,
                                    cos, sin, k_pages, v_pages, block_tables, page_tokens,
-                                   out_dtype == torch.bfloat16, zero)
-        if not zero:
-            self._release(qkv)
+                                   out_dtype == torch.bfloat16)
         self.launches += 1
         return q
 

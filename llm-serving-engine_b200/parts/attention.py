@@ -19,7 +19,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any
 
-from .base import MIXERS, POSITION_ENCODINGS, Mixer, PagedKVNeed, ParamDecl
+from .base import MIXERS, POSITION_ENCODINGS, Mixer, PagedKVNeed, ParamDecl, project_into
 
 
 @dataclass(frozen=True)
@@ -91,14 +91,13 @@ class PagedAttention(Mixer):
 
     accepts_residual = True
 
-    def forward(self, h, step, cache, residual=None):
+    def forward(self, h, step, cache, residual=None, may_defer=False):
         s = self.spec
         ops = self.ops
-        qkv = ops.linear(h, self.qkv_weight, self.qkv_bias)
         tables = step.block_tables[cache.group]
         cos, sin = self.rotary if self.rotary is not None else (None, None)
-        q = ops.rope_kv_write(
-            qkv,
+        q = ops.project_rope_kv_write(
+            h, self.qkv_weight, self.qkv_bias,
             num_heads=s.num_heads,
             num_kv_heads=s.num_kv_heads,
             head_dim=s.head_dim,
@@ -126,5 +125,4 @@ class PagedAttention(Mixer):
             step=step,
             plan=step.plans[self.plan_key()],
         )
-        return ops.linear(o, self.o_weight, self.o_bias, out_dtype=self.env.residual_dtype,
-                          accumulate_into=residual)
+        return project_into(ops, o, self.o_weight, self.o_bias, self.env.residual_dtype, residual, may_defer)

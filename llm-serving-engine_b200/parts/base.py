@@ -150,7 +150,9 @@ class Mixer(Part):
 
     A mixer (or feed-forward) class with ``accepts_residual = True`` is also handed the float32
     residual stream as ``residual=x``; it may add its result into it and return None instead of
-    returning the result.
+    returning the result. A block that can pass on a *pending* add also says ``may_defer=True``:
+    the part may then return an object with a ``resolve()`` method (the kernel set's pending sums)
+    which the block hands to the norm that reads ``x`` next, see :func:`settle`.
 
     ``cache_need()`` says what the mixer keeps per request (None for nothing).
     ``plan_step(host_step, group) -> dict[str, np.ndarray]`` may return int32 work lists that are
@@ -214,6 +216,25 @@ class Block(Part):
 
     def forward(self, x, pending, step, cache):  # pragma: no cover - interface
         raise NotImplementedError
+
+
+def project_into(ops, a, w, bias, out_dtype, residual, may_defer: bool = False):
+    """A branch's output projection ``a @ w.T (+ bias)``: added into ``residual`` (the float32
+    stream) where one is given. Returns None (added), the product, or pending sums (only if
+    ``may_defer``)."""
+    if residual is None:
+        return ops.linear(a, w, bias, out_dtype=out_dtype)
+    if may_defer and getattr(ops, "defers_adds", False):
+        return ops.linear(a, w, bias, out_dtype=out_dtype, accumulate_into=residual, may_defer=True)
+    return ops.linear(a, w, bias, out_dtype=out_dtype, accumulate_into=residual)
+
+
+def settle(pending, norm):
+    """What ``norm`` can take as its ``residual``: pending sums are handed on only to a norm that
+    declares ``takes_pending_sums``; for any other they are added now."""
+    if hasattr(pending, "resolve") and not getattr(norm, "takes_pending_sums", False):
+        return pending.resolve()
+    return pending
 
 
 # --------------------------------------------------------------------------- registries

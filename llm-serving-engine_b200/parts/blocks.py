@@ -5,7 +5,8 @@
     x <- x + mixer(norm_in(x));   x <- x + feed_forward(norm_post(x))
 
 The residual stream ``x`` is float32 and is updated in place; each add is carried out by the norm
-that reads ``x`` next, so a block returns its feed-forward output as ``pending``.
+that reads ``x`` next, so a block returns its feed-forward output as ``pending``: a tensor, None
+(already added), or pending sums of the kernel set (see ``parts.base.settle``).
 """
 
 from __future__ import annotations
@@ -13,7 +14,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, settle
 
 
 @dataclass(frozen=True)
@@ -41,12 +42,12 @@ class PreNormBlock(Block):
         self.feed_forward = self.children["feed_forward"]
 
     def forward(self, x, pending, step, cache):
-        h = self.norm_in.forward(x, pending)
+        h = self.norm_in.forward(x, settle(pending, self.norm_in))
         if getattr(self.mixer, "accepts_residual", False):
-            a = self.mixer.forward(h, step, cache, residual=x)  # None: already added into x
+            a = self.mixer.forward(h, step, cache, residual=x, may_defer=True)  # None: already added into x
         else:
             a = self.mixer.forward(h, step, cache)
-        h = self.norm_post.forward(x, a)
+        h = self.norm_post.forward(x, settle(a, self.norm_post))
         if getattr(self.feed_forward, "accepts_residual", False):
-            return x, self.feed_forward.forward(h, step, residual=x)
+            return x, self.feed_forward.forward(h, step, residual=x, may_defer=True)
         return x, self.feed_forward.forward(h, step)

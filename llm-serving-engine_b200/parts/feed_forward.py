@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from .base import FEED_FORWARDS, FeedForward, ParamDecl
+from .base import FEED_FORWARDS, FeedForward, ParamDecl, project_into
 
 
 @dataclass(frozen=True)
@@ -35,9 +35,7 @@ class SwiGLU(FeedForward):
 
     accepts_residual = True
 
-    def forward(self, h, step, residual=None):
+    def forward(self, h, step, residual=None, may_defer=False):
         ops = self.ops
-        gu = ops.linear(h, self.gate_up_weight, None)
-        a = ops.silu_mul(gu, out_dtype=self.env.dtype)
-        return ops.linear(a, self.down_weight, None, out_dtype=self.env.residual_dtype,
-                          accumulate_into=residual)
+        a = ops.gated_silu(h, self.gate_up_weight, None, out_dtype=self.env.dtype)
+        return project_into(ops, a, self.down_weight, None, self.env.residual_dtype, residual, may_defer)

@@ -21,6 +21,8 @@ class RMSNormSpec:
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
+    takes_pending_sums = True  # the kernel adds a product's pending sums as it reads the row
+
     def param_decls(self):
         return {"weight": ParamDecl((self.spec.size,), "scale")}
 

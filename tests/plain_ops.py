@@ -74,7 +74,14 @@ class PlainOps:
             return None
         return y.to(out_dtype or a.dtype)
 
+    def gated_silu(self, h, w, bias=None, out_dtype=None):
+        return self.silu_mul(self.linear(h, w, bias, out_dtype=torch.float32), out_dtype=out_dtype or h.dtype)
+
     # ------------------------------------------------------------------ attention
+    def project_rope_kv_write(self, h, w, bias, *, out_dtype=None, **kw):
+        qkv = self.linear(h, w, bias, out_dtype=torch.float32)
+        return self.rope_kv_write(qkv, out_dtype=out_dtype or h.dtype, **kw)
+
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
                       cos, sin, k_pages, v_pages, block_tables, page_tokens, out_dtype=None):
         T, D = qkv.shape[0], head_dim

@@ -20,6 +20,22 @@ def llm(folder, name, dtype, **kw):
     return LLM(str(folder), **d)
 
 
+def assert_same_or_near_tie(folder, prompt, a, b):
+    """Two bfloat16 runs of one greedy request through different kernels (a captured step is a
+    padded batch, whose matrix products go to the library where the unpadded step's run this
+    package's kernel) round differently, so they may part where two candidates are nearly tied.
+    Up to there they must agree, and at the parting both choices must be within bfloat16
+    rounding of the plain model's best; after it the sequences are different requests."""
+    if a == b:
+        return
+    assert len(a) == len(b)
+    i = next(k for k in range(len(a)) if a[k] != b[k])
+    logits = plain_llama.model_logits(folder, list(prompt) + a[:i])[-1]
+    bound = 0.03 * float(logits.abs().max())
+    assert float(logits.max() - logits[a[i]]) <= bound and float(logits.max() - logits[b[i]]) <= bound, \
+        (i, a[i], b[i], float(logits.max()), float(logits[a[i]]), float(logits[b[i]]))
+
+
 def greedy(n):
     from llmserve_b200 import SamplingParams
 
@@ -44,7 +60,7 @@ def test_greedy_bfloat16_picks_tokens_the_plain_model_also_ranks_first(sharp_dir
         logits = plain_llama.model_logits(sharp_dirs[name], p + gen)[len(p) - 1 : -1]
         chosen = logits.gather(1, torch.tensor(gen)[:, None])[:, 0]
         gap = logits.max(-1).values - chosen
-        assert (gap <= 0.03 * logits.abs().max()).all(), gap
+        assert (gap <= 0.03 * logits.abs().max(-1).values).all(), gap  # each step by its own largest logit
 
 
 def test_graphs_portions_and_preemption_give_the_same_tokens(sharp_dirs):
@@ -60,8 +76,9 @@ def test_graphs_portions_and_preemption_give_the_same_tokens(sharp_dirs):
     assert tight.engine.stats()["kernel_set"] == "cuda-sm100a"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "C"])
-def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name):
+def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name, dtype):
     """Steps that mix portions of prompts with single tokens, replayed as captured graphs of a
     padded batch (one-token rows first, then portion slots; padding sequences on the spare page):
     same tokens as the same steps run kernel by kernel. Greedy rows, a seeded temperature row (the
@@ -82,7 +99,7 @@ def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name):
         params[3] = special
         runs = {}
         for graphs in (False, True):
-            m = llm(sharp_dirs[name], name, "float32", cuda_graphs=graphs, max_num_batched_tokens=24,
+            m = llm(sharp_dirs[name], name, dtype, cuda_graphs=graphs, max_num_batched_tokens=24,
                     num_kv_blocks=200)
             if graphs:
                 m.engine.runner._graphs().capture_after = 1
@@ -94,10 +111,18 @@ def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name):
                 assert any(not g.sampled for g in mixed) == (special is penal)
                 m.engine.manager.check_invariants()
                 assert m.engine.manager.usage() == 0.0
-        assert runs[True] == runs[False]
+        if dtype == "float32":
+            assert runs[True] == runs[False]
+        else:
+            for k, (a, b) in enumerate(zip(runs[True], runs[False])):
+                if k == 3:  # the sampled / penalised row: same length, tokens not comparable at a parting
+                    assert len(a) == len(b)
+                else:
+                    assert_same_or_near_tie(sharp_dirs[name], prompts[k], a, b)
 
 
-def test_random_arrivals_give_the_same_tokens_with_and_without_graphs(sharp_dirs):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_arrivals_give_the_same_tokens_with_and_without_graphs(sharp_dirs, dtype):
     """Requests of every sampling kind arrive at random moments into a cache so small that some are
     preempted; every step that can be captured is (decode steps, steps with portions, rows sampled
     inside and outside the capture). Token for token the same as with every kernel launched alone."""
@@ -106,7 +131,7 @@ def test_random_arrivals_give_the_same_tokens_with_and_without_graphs(sharp_dirs
     from llmserve_b200 import EngineConfig, LLMEngine, SamplingParams
 
     def run(graphs):
-        eng = LLMEngine(EngineConfig(model=str(sharp_dirs["C"]), dtype="float32", block_size=32,
+        eng = LLMEngine(EngineConfig(model=str(sharp_dirs["C"]), dtype=dtype, block_size=32,
                                      num_kv_blocks=26, max_model_len=1024, max_num_seqs=8,
                                      max_num_batched_tokens=48, cuda_graphs=graphs))
         if graphs:
@@ -125,10 +150,12 @@ def test_random_arrivals_give_the_same_tokens_with_and_without_graphs(sharp_dirs
                 sp = SamplingParams(temperature=0.7, seed=i, logprobs=2, max_tokens=n_out, ignore_eos=True)
             todo.append(([rng.randrange(515) for _ in range(rng.choice([3, 17, 40, 90, 200]))], sp))
         outs, steps = {}, 0
+        asked.clear()
         while todo or eng.has_unfinished_requests():
             for _ in range(rng.randrange(0, 3)):
                 if todo:
-                    eng.add_request(*todo.pop(0))
+                    prompt, sp = todo.pop(0)
+                    asked[eng.add_request(prompt, sp)] = (prompt, sp)
             for o in eng.step():
                 if o.finished:
                     outs[o.request_id] = o.outputs[0].token_ids
@@ -139,9 +166,18 @@ def test_random_arrivals_give_the_same_tokens_with_and_without_graphs(sharp_dirs
         assert eng.manager.usage() == 0.0
         return outs, eng
 
+    asked = {}
     plain, _ = run(False)
     captured, eng = run(True)
-    assert len(plain) == 36 and captured == plain
+    assert len(plain) == 36 and set(captured) == set(plain)
+    if dtype == "float32":
+        assert captured == plain
+    else:
+        for rid, (prompt, sp) in asked.items():
+            if sp.greedy and not sp.has_penalties:
+                assert_same_or_near_tie(sharp_dirs["C"], prompt, captured[rid], plain[rid])
+            else:
+                assert len(captured[rid]) == len(plain[rid])
     held = eng.runner.decode_graphs.graphs.values()
     assert sum(1 for g in held if g.slots) >= 3 and sum(1 for g in held if not g.slots) >= 3
     assert eng.scheduler.num_preemptions > 0
@@ -157,11 +193,13 @@ def test_seeded_sampling_is_the_same_alone_and_in_a_busy_batch(sharp_dirs, dtype
     params = [SamplingParams(temperature=1.0, max_tokens=9, ignore_eos=True), sp,
               SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)]
     outs = busy.generate([PROMPTS[0], PROMPTS[1], PROMPTS[2]], params)
-    if dtype == "float32":
-        assert outs[1].outputs[0].token_ids == want
-    else:  # a bfloat16 batch may round a near-tie the other way; the prefix must still agree
-        assert outs[1].outputs[0].token_ids[:3] == want[:3]
+    assert outs[1].outputs[0].token_ids == want
     assert len(set(want)) > 1
+    # and the busy batch itself gives the same tokens every time it is run (its first request has
+    # no seed and draws one)
+    again = llm(sharp_dirs["C"], "C", dtype, max_num_batched_tokens=8).generate(
+        [PROMPTS[0], PROMPTS[1], PROMPTS[2]], params)
+    assert [o.outputs[0].token_ids for o in again[1:]] == [o.outputs[0].token_ids for o in outs[1:]]
 
 
 def test_penalties_bans_and_logprobs_with_and_without_graphs(sharp_dirs):
@@ -214,11 +252,9 @@ def test_running_ahead_changes_nothing(sharp_dirs, dtype):
         outs[ahead] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason) for o in res]
         m.engine.manager.check_invariants()
         assert m.engine.manager.usage() == 0.0
+    assert outs[True] == outs[False]
     if dtype == "float32":
-        assert outs[True] == outs[False]
         assert outs[True][0][0] == free[: free.index(stop) + 1] and outs[True][0][1] == "stop"
-    else:  # bfloat16 sums are order-dependent (atomics): lengths and reasons must still agree
-        assert [(len(t), r) for t, r in outs[True][1:]] == [(len(t), r) for t, r in outs[False][1:]]
     assert [len(t) for t, _ in outs[True]][1:] == [17, 25, 30]
 
 

@@ -152,6 +152,82 @@ def test_skinny_gemm_sees_every_k_and_every_row(ops):
         assert torch.equal(got, a.float() @ w.float().T), k
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 2048, 2048), (8, 6144, 2048), (13, 1000, 8192), (32, 49152, 960),
+                                   (17, 136, 1000), (5, 128, 64)])
+def test_few_rows_product_gives_the_same_bits_every_run_and_in_every_batch(ops, T, N, K):
+    """A tile's sum over k is shared between blocks and added up in a fixed order: two runs agree
+    bit for bit, and a row alone gives the bits it gives among other rows (16- and 32-column tiles)."""
+    a, w = rnd(T, K, dtype=torch.bfloat16, seed=1).cuda(), rnd(N, K, dtype=torch.bfloat16, seed=2).cuda()
+    first = ops.linear(a, w, None, out_dtype=torch.float32)
+    for _ in range(3):
+        assert torch.equal(ops.linear(a, w, None, out_dtype=torch.float32), first)
+    t = T // 2
+    assert torch.equal(ops.linear(a[t : t + 1].contiguous(), w, None, out_dtype=torch.float32)[0], first[t])
+    x = rnd(T, N, seed=3).cuda()
+    x1, x2 = x.clone(), x.clone()
+    ops.linear(a, w, None, accumulate_into=x1)
+    ops.linear(a, w, None, accumulate_into=x2)
+    assert torch.equal(x1, x2) and torch.equal(x1, x + first)
+    ops.check_kernel_errors()
+
+
+@pytest.mark.parametrize("T,I,K", [(1, 64, 64), (8, 2560, 960), (17, 160, 200), (32, 100, 520),
+                                   (3, 8192, 2048), (16, 272, 192)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gated_silu_in_the_product_kernel(ops, T, I, K, bias):
+    """Gate rows and their up rows meet in one tile (two boxes of 64 rows); the gate reaches its
+    activation as a float32 sum. Intermediate sizes that are no multiple of 64 leave a ragged tile."""
+    h = rnd(T, K, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * I, K, dtype=torch.bfloat16, seed=2, scale=0.2)
+    b = rnd(2 * I, dtype=torch.bfloat16, seed=3) if bias else None
+    got = ops.gated_silu(h.cuda(), w.cuda(), None if b is None else b.cuda(), out_dtype=torch.bfloat16)
+    assert got.dtype == torch.bfloat16 and got.shape == (T, I)
+    gu = h.double() @ w.double().T + (0 if b is None else b.double())
+    g, u = gu[:, :I], gu[:, I:]
+    ref = g / (1 + torch.exp(-g)) * u
+    assert (got.double().cpu() - ref).abs().max() <= 2.0**-7 * ref.abs().max()
+    again = ops.gated_silu(h.cuda(), w.cuda(), None if b is None else b.cuda(), out_dtype=torch.bfloat16)
+    assert torch.equal(got, again)
+    ops.check_kernel_errors()
+
+
+@pytest.mark.parametrize("nq,nk,D,page", [(4, 2, 16, 16), (4, 1, 32, 8), (6, 2, 64, 32), (15, 5, 64, 16),
+                                          (32, 32, 64, 16), (8, 2, 128, 48), (3, 1, 48, 16)])
+@pytest.mark.parametrize("bias,rope,writes", [(False, True, True), (True, True, True),
+                                              (False, False, True), (False, True, False)])
+def test_projection_rotation_and_cache_write_in_one_kernel(ops, nq, nk, D, page, bias, rope, writes):
+    """q|k|v projection, rotation and the write of k and v into shuffled pages, against the plain
+    product followed by the plain rotation; head size 48 (no whole heads per tile) takes the
+    two-kernel path. Untouched cache slots must keep their stale contents."""
+    K = 200
+    q_lens, ctx_lens = [1, 1, 1, 1, 1], [30, 1, 17, 64, 9]
+    _, kp, vp, tables, positions, token_seq, _ = paged_case(5, q_lens, ctx_lens, nq, nk, D, page,
+                                                            torch.bfloat16, seed=4)
+    T = sum(q_lens)
+    h = rnd(T, K, dtype=torch.bfloat16, seed=5)
+    w = rnd((nq + 2 * nk) * D, K, dtype=torch.bfloat16, seed=6, scale=0.1)
+    b = rnd((nq + 2 * nk) * D, dtype=torch.bfloat16, seed=7) if bias else None
+    ang = torch.outer(torch.arange(80, dtype=torch.float64), 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float64) / D)))
+    cos, sin = (ang.cos().float(), ang.sin().float()) if rope else (None, None)
+    kw = dict(num_heads=nq, num_kv_heads=nk, head_dim=D, positions=positions, token_seq=token_seq,
+              block_tables=tables, page_tokens=page, out_dtype=torch.bfloat16)
+    kp_ref, vp_ref = kp.clone(), vp.clone()
+    q_ref = PlainOps().project_rope_kv_write(h, w, b, cos=cos, sin=sin, k_pages=kp_ref if writes else None,
+                                             v_pages=vp_ref if writes else None, **kw)
+    dev = lambda t: None if t is None else t.cuda()
+    kp_g, vp_g = kp.cuda(), vp.cuda()
+    gkw = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in kw.items()}
+    q_g = ops.project_rope_kv_write(dev(h), dev(w), dev(b), cos=dev(cos), sin=dev(sin),
+                                    k_pages=kp_g if writes else None, v_pages=vp_g if writes else None, **gkw)
+    assert q_g.dtype == torch.bfloat16 and q_g.shape == (T, nq * D)
+    close(q_g, q_ref, "bfloat16", rel16=0.005)
+    close(kp_g, kp_ref, "bfloat16", rel16=0.005)
+    close(vp_g, vp_ref, "bfloat16", rel16=0.005)
+    if not writes:
+        assert torch.equal(kp_g.cpu(), kp) and torch.equal(vp_g.cpu(), vp)
+    ops.check_kernel_errors()
+
+
 def paged_case(nseq, q_lens, ctx_lens, nq, nk, D, page, dtype, seed=0, shuffle=True):
     """Random q/k/v rows, a cache whose pages are handed out in shuffled order."""
     g = torch.Generator().manual_seed(seed)

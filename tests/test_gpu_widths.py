@@ -170,12 +170,14 @@ def test_requests_decoding_side_by_side(wide_dirs, oracles, name, batch, ctx, dt
     check(got, reqs, oracles[name], dtype)
 
 
-def test_sharp_attention_at_real_widths(wide_dirs, tmp_path):
+@pytest.mark.parametrize("dtype,factor", [("float32", 4.0), ("bfloat16", 2.0)])
+def test_sharp_attention_at_real_widths(wide_dirs, tmp_path, dtype, factor):
     """With random weights of deviation 0.02 the attention weights are nearly flat, and a key that
-    is left out moves the logits little. Here the query and key projections are four times larger,
-    so the scores are sixteen times larger and every query's softmax is dominated by a few keys
-    anywhere among its 2300: a partition, a tile or a page that is dropped or read twice then
-    changes the logits far beyond rounding."""
+    is left out moves the logits little. Here the query and key projections are ``factor`` times
+    larger, so the scores are ``factor`` squared times larger and every query's softmax is
+    dominated by a few keys anywhere among its 2300: a partition, a tile or a page that is dropped
+    or read twice then changes the logits far beyond rounding. (bfloat16 keeps eight bits of a
+    query and a key, so an error of a score grows with the score; its factor is the smaller one.)"""
     import shutil
 
     from safetensors.torch import load_file, save_file
@@ -185,13 +187,16 @@ def test_sharp_attention_at_real_widths(wide_dirs, tmp_path):
     t = load_file(str(wide_dirs[name] / "model.safetensors"))
     for k in t:
         if k.endswith("q_proj.weight") or k.endswith("k_proj.weight"):
-            t[k] = (t[k].float() * 4).to(t[k].dtype)
+            t[k] = (t[k].float() * factor).to(t[k].dtype)
     save_file(t, str(tmp_path / "model.safetensors"))
     del t
     reqs = requests_of(name, [2300], seed=77)
     oracle = Oracle(tmp_path)
-    for dtype in ("float32", "bfloat16"):
-        for steps in (traces.whole(reqs), traces.decode_tail(reqs, tail=32),
-                      traces.portions(reqs, sizes=(900, 2, 513, 33, 700))):
-            runner = runner_for(tmp_path, dtype, traces.tokens_needed(reqs))
+    cuts = {"whole": traces.whole(reqs), "decode_tail": traces.decode_tail(reqs, tail=32),
+            "portions": traces.portions(reqs, sizes=(900, 2, 513, 33, 700))}
+    for cut, steps in cuts.items():
+        runner = runner_for(tmp_path, dtype, traces.tokens_needed(reqs))
+        try:
             check(traces.replay(runner, only_wanted(steps, reqs)), reqs, oracle, dtype)
+        except AssertionError as e:
+            raise AssertionError(f"{cut}: {e}") from None

@@ -1,24 +1,31 @@
-"""Command-line entry point: ``python -m llmserve_b200 <command> ...`` (src/llmserve/cli.py)."""
+"""``python -m llmserve_b200 <command> ...``: the commands of this package under one name, as the
+reference has them under ``llmserve`` (src/llmserve/cli.py). A command's module is imported only
+when that command runs, so ``--help`` needs no GPU."""
 
 from __future__ import annotations
 
+import argparse
 import importlib
 import sys
 
-COMMANDS = {
-    "generate": ("llmserve_b200.generate_cli", "generate tokens or text from the command line"),
-    "random-model": ("llmserve_b200.random_model_cli", "write a random-weights model folder"),
-}
+
+def _commands(sub) -> None:
+    """Each command: its name, the module whose ``main(argv)`` runs it, one line of help."""
+    for name, module, about in (
+        ("generate", "llmserve_b200.generate_cli", "generate tokens or text from the command line"),
+        ("random-model", "llmserve_b200.random_model_cli", "write a random-weights model folder"),
+    ):
+        sub.add_parser(name, help=about, add_help=False).set_defaults(module=module)
 
 
 def main(argv: list[str] | None = None) -> None:
-    argv = sys.argv[1:] if argv is None else argv
-    if not argv or argv[0] in ("-h", "--help") or argv[0] not in COMMANDS:
-        print("usage: llmserve_b200 <command> [args]\n\ncommands:")
-        for name, (_, helptext) in COMMANDS.items():
-            print(f"  {name:14s} {helptext}")
-        sys.exit(0 if argv and argv[0] in ("-h", "--help") else 1)
-    importlib.import_module(COMMANDS[argv[0]][0]).main(argv[1:])
+    parser = argparse.ArgumentParser(prog="llmserve_b200", description=__doc__.split(":")[1].strip())
+    _commands(parser.add_subparsers(dest="command", metavar="<command>"))
+    args, rest = parser.parse_known_args(sys.argv[1:] if argv is None else argv)
+    if args.command is None:
+        parser.print_help()
+        sys.exit(1)
+    importlib.import_module(args.module).main(rest)
 
 
 if __name__ == "__main__":

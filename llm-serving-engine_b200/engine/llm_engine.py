@@ -6,6 +6,7 @@ Names and meanings follow src/llmserve/engine.py (``EngineConfig`` :30-66, ``LLM
 
 from __future__ import annotations
 
+import contextlib
 import itertools
 import random
 import time
@@ -16,10 +17,10 @@ from ..models.hub import preset_config_dict, resolve_model_path
 from ..sampling import Sampler, SampleRow, SamplingParams
 from ..weights.random_init import random_parameters
 from .batch import StepEntry
-from .detokenizer import IncrementalDetokenizer, find_stop
+from .detokenizer import TextStream, find_stop
 from .runner import ModelRunner, build_model, load_model, resolve_dtype
 from .scheduler import Scheduler, SchedulerConfig
-from .sequence import CompletionOutput, Request, RequestOutput, Sequence
+from .sequence import Request, RequestOutput, Sequence
 
 
 @dataclass
@@ -39,6 +40,7 @@ class EngineConfig:
     cuda_graphs: bool = True  # replay captured graphs for steps of single tokens only
     run_ahead: bool = True  # launch the next decode step before this one's tokens are read
     warm_up: bool = True  # run a throw-away step at start-up (library handles, kernel modules)
+    profile: bool = False  # time every step on the device with CUDA events and mark it with an NVTX range
     config_overrides: dict | None = None  # config.json keys to replace in a "random:<alias>" model
 
     def scheduler_config(self) -> SchedulerConfig:
@@ -58,12 +60,19 @@ class _InFlight:
         self.sample_seqs = sample_seqs
         self.stats = stats
         self.t0 = t0
+        self.t_launched = t0  # when the step's kernels had been enqueued
+        self.gpu_events = None  # (before, after) the step on the stream, with EngineConfig.profile
         self.pending = None  # handle of a launched CUDA-graph step
         self.result = None  # SamplerOutput of a step that ran synchronously
 
 
 @dataclass
 class StepStats:
+    """What the last finished step did and where its time went. The ``t_*`` are host wall-clock
+    seconds (names of src/llmserve/engine.py:70-80); ``gpu_ms`` is the device time between the
+    step's launch and the end of its sampling, from CUDA events, when ``EngineConfig.profile`` is
+    set (it costs a synchronisation per step)."""
+
     num_seqs: int = 0
     num_tokens: int = 0
     num_prefill_tokens: int = 0
@@ -71,9 +80,10 @@ class StepStats:
     num_preempted: int = 0
     step_time: float = 0.0
     t_schedule: float = 0.0
-    t_forward: float = 0.0  # input preparation, model forward, sampling kernels, token read-back
-    t_sample: float = 0.0
-    t_postprocess: float = 0.0
+    t_forward: float = 0.0  # building the batch, uploading it, launching the model's kernels
+    t_sample: float = 0.0  # waiting for the device and reading the sampled tokens back
+    t_postprocess: float = 0.0  # appending tokens, text, stop checks, output objects
+    gpu_ms: float | None = None
 
 
 class LLMEngine:
@@ -120,7 +130,6 @@ class LLMEngine:
         self.manager = self.runner.manager
         self.scheduler = Scheduler(cfg.scheduler_config(), self.manager)
         self.sampler = Sampler(ops, cfg.device, max_slots=self.manager.max_requests)
-        self.detok = IncrementalDetokenizer(tokenizer) if tokenizer is not None else None
         self.requests: dict[str, Request] = {}
         self._seq_ids = itertools.count()
         self._req_ids = itertools.count()
@@ -156,45 +165,52 @@ class LLMEngine:
     # ------------------------------------------------------------------ intake
     def add_request(self, prompt: str | list[int], params: SamplingParams | None = None,
                     request_id: str | None = None, arrival_time: float | None = None) -> str:
+        """Queue a prompt (text, if the engine has a tokenizer, or token ids). Returns the request's
+        id. A request that could never run is refused here (src/llmserve/engine.py:237-245)."""
         params = params or SamplingParams()
-        if isinstance(prompt, str):
-            if self.tokenizer is None:
-                raise ValueError("text prompts need a tokenizer")
-            ids = list(self.tokenizer(prompt, add_special_tokens=False).input_ids)
-            text = prompt
-        else:
-            ids, text = [int(t) for t in prompt], None
-        if not ids:
-            raise ValueError("empty prompt")
-        if len(ids) >= self.cfg.max_model_len:
-            raise ValueError(f"prompt has {len(ids)} tokens; max_model_len is {self.cfg.max_model_len}")
-        v = self.model_cfg.vocab_size
-        if min(ids) < 0 or max(ids) >= v:
-            raise ValueError(f"prompt token ids must lie in [0, {v})")
-        total = min(len(ids) + params.max_tokens, self.cfg.max_model_len)
-        if not self.manager.fits_at_all(total, self.cfg.max_num_batched_tokens):
-            raise ValueError("request can never fit in the KV cache; raise kv_cache_memory_gb")
-        rid = request_id or f"req-{next(self._req_ids)}"
+        text, ids = self._token_ids(prompt)
+        self._refuse_what_can_never_run(ids, params)
+        rid = request_id if request_id else f"req-{next(self._req_ids)}"
         if rid in self.requests:
             raise ValueError(f"duplicate request id {rid}")
-        req = Request(rid, text, ids, params, arrival_time)
-        seed = params.seed if params.seed is not None else self._seed_source.getrandbits(63)
-        seq = Sequence(next(self._seq_ids), req, ids, seed)
-        if self.detok is not None:
-            seq.detok_state = self.detok.init_state(ids)
-        req.seqs.append(seq)
-        self.requests[rid] = req
+        request = Request(rid, text, ids, params, arrival_time)
+        # a request without a seed draws one, so that its samples too come from the device
+        # generator keyed by (seed, token index, vocabulary index)
+        seed = self._seed_source.getrandbits(63) if params.seed is None else params.seed
+        seq = Sequence(next(self._seq_ids), request, ids, seed)
+        if self.tokenizer is not None:
+            seq.text_stream = TextStream(self.tokenizer, ids)
+        request.seqs.append(seq)
+        self.requests[rid] = request
         self.scheduler.add(seq)
         return rid
 
+    def _token_ids(self, prompt) -> tuple[str | None, list[int]]:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("text prompts need a tokenizer")
+            return prompt, list(self.tokenizer(prompt, add_special_tokens=False).input_ids)
+        return None, [int(t) for t in prompt]
+
+    def _refuse_what_can_never_run(self, ids: list[int], params: SamplingParams) -> None:
+        limit, vocab = self.cfg.max_model_len, self.model_cfg.vocab_size
+        if not ids:
+            raise ValueError("empty prompt")
+        if len(ids) >= limit:
+            raise ValueError(f"prompt has {len(ids)} tokens; max_model_len is {limit}")
+        if min(ids) < 0 or max(ids) >= vocab:
+            raise ValueError(f"prompt token ids must lie in [0, {vocab})")
+        longest = min(len(ids) + params.max_tokens, limit)
+        if not self.manager.fits_at_all(longest, self.cfg.max_num_batched_tokens):
+            raise ValueError("request can never fit in the KV cache; raise kv_cache_memory_gb")
+
     def abort_request(self, request_id: str) -> None:
-        req = self.requests.pop(request_id, None)
-        if req is None:
-            return
-        for s in req.seqs:
-            if not s.is_finished:
-                s.finish_reason = "abort"
-                self.scheduler.finish(s)
+        """Stop a request wherever it is; what it holds is given back at once. Unknown ids are ignored."""
+        request = self.requests.pop(request_id, None)
+        for seq in (request.seqs if request is not None else ()):
+            if not seq.is_finished:
+                seq.finish_reason = "abort"
+                self.scheduler.finish(seq)
 
     def has_unfinished_requests(self) -> bool:
         return self.scheduler.has_unfinished()
@@ -251,11 +267,32 @@ class LLMEngine:
         rows = [self._sample_row(seq) for seq in sample_seqs]
         scheduled = [(s.seq, s.num_new_tokens) for s in sched.scheduled]
         flight = _InFlight(scheduled, sample_seqs, stats, t0)
-        if self.cfg.cuda_graphs and self.runner.can_launch_decode(entries, rows):
-            flight.pending = self.runner.launch_decode(entries, rows, sampler=self.sampler)
-        else:
-            flight.result = self.runner.step_and_sample(entries, self.sampler, rows, graphs=False)
+        with self._profiled(flight, sum(n for _, n in scheduled)):
+            if self.cfg.cuda_graphs and self.runner.can_launch_decode(entries, rows):
+                flight.pending = self.runner.launch_decode(entries, rows, sampler=self.sampler)
+            else:
+                flight.result = self.runner.step_and_sample(entries, self.sampler, rows, graphs=False)
+        flight.t_launched = time.monotonic()
         return flight
+
+    @contextlib.contextmanager
+    def _profiled(self, flight: "_InFlight", tokens: int):
+        """With ``EngineConfig.profile``: CUDA events around the step's work on the stream and an
+        NVTX range around its launch, so a timeline shows which kernels belong to which step."""
+        if not (self.cfg.profile and self.runner.device.type == "cuda"):
+            yield
+            return
+        import torch
+
+        before, after = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.nvtx.range_push(f"step {self.total_steps}: {len(flight.scheduled)} sequences, {tokens} tokens")
+        before.record()
+        try:
+            yield
+        finally:
+            after.record()
+            torch.cuda.nvtx.range_pop()
+            flight.gpu_events = (before, after)
 
     def _launch_ahead(self, cur: "_InFlight"):
         """Launch the step after ``cur`` before ``cur``'s tokens are known, if the batch cannot change."""
@@ -285,7 +322,9 @@ class LLMEngine:
             self.manager.allocate(seq.seq_id, 2)
         t0 = time.monotonic()
         flight = _InFlight([(seq, 1) for seq in seqs], list(seqs), StepStats(), t0)
-        flight.pending = self.runner.launch_decode(entries, rows, ahead_of=cur.pending)
+        with self._profiled(flight, len(seqs)):
+            flight.pending = self.runner.launch_decode(entries, rows, ahead_of=cur.pending)
+        flight.t_launched = time.monotonic()
         return flight
 
     def _pages_for_all(self, seqs, n: int) -> bool:
@@ -302,10 +341,15 @@ class LLMEngine:
     def _finish_step(self, cur: "_InFlight"):
         """Read the step's tokens and do the host's part. Returns (outputs, batch unchanged)."""
         stats = cur.stats
-        t1 = time.monotonic()
+        t_wait = time.monotonic()
         result = self.runner.collect_decode(cur.pending) if cur.pending is not None else cur.result
         tokens, logprobs, tops = result.token_ids, result.logprobs, result.top_logprobs
-        stats.t_forward = time.monotonic() - t1
+        t_host = time.monotonic()
+        stats.t_forward = cur.t_launched - cur.t0 - stats.t_schedule
+        stats.t_sample = t_host - t_wait
+        if cur.gpu_events is not None:
+            cur.gpu_events[1].synchronize()
+            stats.gpu_ms = cur.gpu_events[0].elapsed_time(cur.gpu_events[1])
         unchanged = True
         for seq, n in cur.scheduled:
             if seq.is_finished:  # aborted while the step ran
@@ -317,28 +361,34 @@ class LLMEngine:
                 stats.num_decode_tokens += 1
             else:
                 stats.num_prefill_tokens += n
-        now = time.monotonic()
         touched: dict[str, Request] = {}
         for j, seq in enumerate(cur.sample_seqs):
             if seq.is_finished:
                 continue
-            self._append_token(seq, tokens[j], None if logprobs is None else logprobs[j],
-                               None if tops is None else tops[j], now)
-            touched[seq.request.request_id] = seq.request
-            if seq.is_finished:
+            seq.request.metrics.token_at(t_host)
+            seq.output_token_ids.append(tokens[j])
+            if logprobs is not None:
+                seq.logprobs.append(logprobs[j])
+                seq.top_logprobs.append(tops[j])
+            reason = self._why_finished(seq, tokens[j])
+            if reason is not None:
+                seq.finish_reason = reason
+                self.scheduler.finish(seq)
                 unchanged = False
+            touched[seq.request.request_id] = seq.request
+        outputs = []
+        for request in touched.values():
+            if request.is_finished:
+                request.metrics.finished_time = t_host
+                self.requests.pop(request.request_id, None)
+            outputs.append(RequestOutput.of(request))
+        done = time.monotonic()
         stats.num_seqs = len(cur.scheduled)
         stats.num_tokens = sum(n for _, n in cur.scheduled)
-        stats.step_time = time.monotonic() - cur.t0
-        stats.t_postprocess = time.monotonic() - now
+        stats.t_postprocess = done - t_host
+        stats.step_time = done - cur.t0
         self.last_step = stats
         self.total_steps += 1
-        outputs = []
-        for req in touched.values():
-            outputs.append(self._make_output(req))
-            if req.is_finished:
-                req.metrics.finished_time = now
-                self.requests.pop(req.request_id, None)
         return outputs, unchanged
 
     def _sample_row(self, seq: Sequence, ahead: int = 0) -> SampleRow:
@@ -354,64 +404,41 @@ class LLMEngine:
                          slot=held.slot if held is not None else -1,
                          epoch=held.epoch if held is not None else 0)
 
-    def _append_token(self, seq, token, logprob, top, now) -> None:
-        req = seq.request
-        if req.metrics.first_token_time is None:
-            req.metrics.first_token_time = now
-        req.metrics.last_token_time = now
-        req.metrics.token_times.append(now)
-        seq.output_token_ids.append(token)
-        if logprob is not None:
-            seq.logprobs.append(logprob)
-            seq.top_logprobs.append(top)
+    def _why_finished(self, seq: Sequence, token: int) -> str | None:
+        """``seq`` has just received ``token``: bring its text up to date and say whether, and
+        why, it ends here. Stops are looked for before the length limits, a stop token before a
+        stop string (the order of src/llmserve/engine.py:475-491)."""
         p = seq.params
-        new_text = ""
-        if self.detok is not None:
-            new_text = self.detok.step(seq.token_ids(), seq.detok_state)
-            seq.output_text += new_text
-        # finish checks in the reference's order (src/llmserve/engine.py:475-491)
-        reason = None
-        if (not p.ignore_eos and token in self.eos_ids) or token in p.stop_token_ids:
-            reason, seq.stop_reason = "stop", token
-        elif p.stop and new_text:
-            hit = find_stop(seq.output_text, len(new_text), p.stop)
+        fresh = ""
+        if seq.text_stream is not None:
+            fresh = seq.text_stream.push(seq.token_ids())
+            seq.output_text += fresh
+        if token in p.stop_token_ids or (token in self.eos_ids and not p.ignore_eos):
+            seq.stop_reason = token
+            return "stop"
+        if fresh and p.stop:
+            hit = find_stop(seq.output_text, len(fresh), p.stop)
             if hit is not None:
-                idx, s = hit
-                seq.output_text = seq.output_text[: idx + (len(s) if p.include_stop_str_in_output else 0)]
-                reason, seq.stop_reason = "stop", s
-        if reason is None and (len(seq.output_token_ids) >= p.max_tokens
-                               or seq.num_tokens >= self.cfg.max_model_len):
-            reason = "length"
-        if reason is not None:
-            seq.finish_reason = reason
-            self.scheduler.finish(seq)
-
-    def _make_output(self, req: Request) -> RequestOutput:
-        outs = [
-            CompletionOutput(
-                index=s.index, text=s.output_text, token_ids=list(s.output_token_ids),
-                finish_reason=s.finish_reason, stop_reason=s.stop_reason,
-                logprobs=list(s.logprobs) if s.params.logprobs is not None else None,
-                top_logprobs=list(s.top_logprobs) if s.params.logprobs is not None else None,
-            )
-            for s in req.seqs
-        ]
-        return RequestOutput(req.request_id, req.prompt, req.prompt_token_ids, outs,
-                             req.is_finished, 0, req.metrics)
+                begins, stop = hit
+                keep = begins + len(stop) if p.include_stop_str_in_output else begins
+                seq.output_text = seq.output_text[:keep]
+                seq.stop_reason = stop
+                return "stop"
+        if len(seq.output_token_ids) >= p.max_tokens or seq.num_tokens >= self.cfg.max_model_len:
+            return "length"
+        return None
 
     def stats(self) -> dict:
-        return {
-            "num_running": len(self.scheduler.running),
-            "num_waiting": len(self.scheduler.waiting),
-            "kv_cache_usage": self.manager.usage(),
-            "num_kv_blocks": self.manager.num_pages(0),
-            "num_preemptions": self.scheduler.num_preemptions,
-            "kernel_set": self.ops.name,
-        }
+        """Counters of the engine as it stands, and the kernel set that really runs."""
+        sched = self.scheduler
+        return dict(num_running=len(sched.running), num_waiting=len(sched.waiting),
+                    num_preemptions=sched.num_preemptions, kv_cache_usage=self.manager.usage(),
+                    num_kv_blocks=self.manager.num_pages(0), kernel_set=self.ops.name)
 
 
 class LLM:
-    """Offline batch API: ``LLM(model="random:smollm2-135m").generate(prompts, params)``."""
+    """Offline use: ``LLM(model="random:smollm2-135m").generate(prompts, params)``
+    (the entry point of src/llmserve/engine.py:536-577)."""
 
     def __init__(self, model: str = "smollm2-135m", ops=None, tokenizer=None, **kwargs) -> None:
         self.engine = LLMEngine(EngineConfig(model=model, **kwargs), ops=ops, tokenizer=tokenizer)
@@ -419,25 +446,26 @@ class LLM:
 
     def generate(self, prompts, params: SamplingParams | list[SamplingParams] | None = None,
                  use_tqdm: bool = False) -> list[RequestOutput]:
-        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
-            prompts = [prompts]
-        if not isinstance(params, list):
-            params = [params or SamplingParams()] * len(prompts)
-        ids = [self.engine.add_request(p, sp) for p, sp in zip(prompts, params, strict=True)]
-        done: dict[str, RequestOutput] = {}
+        """One output per prompt, in the order of the prompts. ``prompts``: a text, a list of
+        token ids, or a list of either; ``params``: one for all, or one per prompt."""
+        one = isinstance(prompts, str) or (len(prompts) > 0 and isinstance(prompts[0], int))
+        batch = [prompts] if one else list(prompts)
+        each = params if isinstance(params, list) else [params or SamplingParams()] * len(batch)
+        if len(each) != len(batch):
+            raise ValueError(f"{len(batch)} prompts but {len(each)} sampling parameters")
+        order = [self.engine.add_request(p, sp) for p, sp in zip(batch, each)]
+        finished: dict[str, RequestOutput] = {}
         while self.engine.has_unfinished_requests():
-            for o in self.engine.step():
-                if o.finished:
-                    done[o.request_id] = o
-        return [done[i] for i in ids]
+            finished.update((o.request_id, o) for o in self.engine.step() if o.finished)
+        return [finished[rid] for rid in order]
 
-    def chat(self, messages_list, params=None, **kw) -> list[RequestOutput]:
+    def chat(self, messages_list, params=None, **template_options) -> list[RequestOutput]:
+        """``generate`` on conversations (lists of ``{"role", "content"}``), through the
+        tokenizer's chat template with the turn of the assistant opened."""
         if self.tokenizer is None:
             raise ValueError("chat needs a tokenizer with a chat template")
         if messages_list and isinstance(messages_list[0], dict):
             messages_list = [messages_list]
-        prompts = [
-            self.tokenizer.apply_chat_template(m, tokenize=False, add_generation_prompt=True, **kw)
-            for m in messages_list
-        ]
-        return self.generate(prompts, params)
+        render = self.tokenizer.apply_chat_template
+        return self.generate([render(m, tokenize=False, add_generation_prompt=True, **template_options)
+                              for m in messages_list], params)

@@ -32,24 +32,22 @@ class SamplingParams:
     def __post_init__(self) -> None:
         if isinstance(self.stop, str):
             self.stop = [self.stop]
-        if self.n != 1:
-            raise ValueError("n must be 1: parallel samples of one prompt are not built")
-        if self.temperature < 0:
-            raise ValueError("temperature must be >= 0")
-        if not 0 < self.top_p <= 1:
-            raise ValueError("top_p must be in (0, 1]")
-        if self.top_k == 0 or self.top_k < -1:
-            raise ValueError("top_k must be -1 (disabled) or >= 1")
-        if not 0 <= self.min_p <= 1:
-            raise ValueError("min_p must be in [0, 1]")
-        if self.repetition_penalty <= 0:
-            raise ValueError("repetition_penalty must be > 0")
-        if self.max_tokens < 1:
-            raise ValueError("max_tokens must be >= 1")
-        if self.min_tokens < 0:
-            raise ValueError("min_tokens must be >= 0")
-        if self.logprobs is not None and not 0 <= self.logprobs <= 20:
-            raise ValueError("logprobs must be between 0 and 20")
+        # (what must hold, what to say if it does not); the ranges are the reference's
+        # (src/llmserve/sampling.py:40-61), n > 1 is refused because it is not built
+        rules = (
+            (self.n == 1, "n must be 1: parallel samples of one prompt are not built"),
+            (self.temperature >= 0, "temperature must be >= 0"),
+            (0 < self.top_p <= 1, "top_p must be in (0, 1]"),
+            (self.top_k == -1 or self.top_k >= 1, "top_k must be -1 (disabled) or >= 1"),
+            (0 <= self.min_p <= 1, "min_p must be in [0, 1]"),
+            (self.repetition_penalty > 0, "repetition_penalty must be > 0"),
+            (self.max_tokens >= 1, "max_tokens must be >= 1"),
+            (self.min_tokens >= 0, "min_tokens must be >= 0"),
+            (self.logprobs is None or 0 <= self.logprobs <= 20, "logprobs must be between 0 and 20"),
+        )
+        for holds, message in rules:
+            if not holds:
+                raise ValueError(message)
 
     @property
     def greedy(self) -> bool:

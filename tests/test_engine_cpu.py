@@ -273,3 +273,72 @@ def test_running_ahead_asks_for_the_pages_of_all_sequences_together(sharp_dirs):
     done = run_all(eng)  # the scheduler preempts where pages run out; nothing raises
     assert len(done) == 3 and eng.scheduler.num_preemptions > 0
     assert len({tuple(o.outputs[0].token_ids) for o in done.values()}) == 1
+
+
+class _ByteTokenizer:
+    """Token = one byte of UTF-8 text: a character can be spread over up to four tokens."""
+
+    eos_token_id = None
+
+    def decode(self, ids, skip_special_tokens=True):
+        return bytes(ids).decode("utf-8", errors="replace")
+
+    def __call__(self, text, add_special_tokens=False):
+        from types import SimpleNamespace
+
+        return SimpleNamespace(input_ids=list(text.encode("utf-8")))
+
+
+class _LetterTokenizer(_ByteTokenizer):
+    """Token id -> one lower-case letter: every token sequence is valid text."""
+
+    def decode(self, ids, skip_special_tokens=True):
+        return "".join(chr(97 + i % 26) for i in ids)
+
+    def __call__(self, text, add_special_tokens=False):
+        from types import SimpleNamespace
+
+        return SimpleNamespace(input_ids=[ord(c) - 97 for c in text])
+
+
+def test_text_stream_shows_whole_characters_only():
+    from llmserve_b200.engine.detokenizer import TextStream, find_stop
+
+    tok = _ByteTokenizer()
+    prompt = list("say: ".encode())
+    text = "héllo wörld → ok 🙂!"
+    ids = prompt + list(text.encode())
+    stream = TextStream(tok, prompt)
+    shown = []
+    for n in range(len(prompt) + 1, len(ids) + 1):
+        piece = stream.push(ids[:n])
+        assert "\N{REPLACEMENT CHARACTER}" not in piece
+        shown.append(piece)
+    assert "".join(shown) == text
+    assert shown.count("") == len(text.encode()) - len(text)  # one silent step per continuation byte
+    assert find_stop("abc STOP def", 5, ["STOP"]) == (4, "STOP")  # ends inside the new text
+    assert find_stop("abc STOP defgh", 5, ["STOP"]) is None  # lies wholly in older text
+    assert find_stop("xxabyy", 4, ["by", "ab", ""]) == (2, "ab")  # the one that begins first
+
+
+def test_stop_strings_cut_the_text(sharp_dirs):
+    from llmserve_b200 import SamplingParams
+
+    tok = _LetterTokenizer()
+
+    def run(**kw):
+        eng = engine(sharp_dirs["A"], "A")
+        eng.tokenizer = tok
+        rid = eng.add_request("hello", SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True, **kw))
+        return run_all(eng)[rid].outputs[0]
+
+    free = run()
+    assert len(free.text) == 12 and free.finish_reason == "length"
+    assert free.token_ids == plain_llama.greedy(sharp_dirs["A"], [ord(c) - 97 for c in "hello"], 12)
+    stop = free.text[5:8]
+    at = free.text.find(stop)
+    cut = run(stop=[stop])
+    assert (cut.text, cut.finish_reason, cut.stop_reason) == (free.text[:at], "stop", stop)
+    assert len(cut.token_ids) == at + 3  # the tokens of the stop string were generated
+    kept = run(stop=[stop], include_stop_str_in_output=True)
+    assert kept.text == free.text[: at + 3]

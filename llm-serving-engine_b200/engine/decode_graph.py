@@ -234,6 +234,8 @@ class DecodeGraphs:
         self.capture_after = 2  # a shape is captured the second time it is asked for
         self.asked: dict[tuple, int] = {}
         self.mixed_plannable = all(hasattr(m, "plan_rows") for m, _ in runner.planners.values())
+        # a part that works from the host while a step runs rules out captures altogether
+        self.capturable = not any(getattr(p, "needs_host_step", False) for p in model.parts())
 
     def padded(self, n: int) -> int:
         """The captured batch size that serves ``n`` rows."""
@@ -278,6 +280,8 @@ class DecodeGraphs:
     def accepts(self, entries: Sequence[StepEntry], rows) -> bool:
         """Should this step run as a captured graph? Steps of single tokens always; steps with
         portions once their shape has been asked for ``capture_after`` times."""
+        if not self.capturable:
+            return False
         if self.forward_usable(entries, rows):
             return True
         shape = self.mixed_shape(entries)
@@ -558,6 +562,8 @@ class DecodeGraphs:
         with the logits and the sampler runs on them before this method returns.
         """
         runner = self.runner
+        if not self.capturable:
+            raise ValueError("this model has a part that works from the host: its steps are not captured")
         if not self.forward_usable(entries, rows):
             if ahead_of is not None:
                 raise ValueError("only a step of single tokens can run ahead")

@@ -1,8 +1,9 @@
 """A decoder-only language model assembled from a :class:`ModelPlan`.
 
 Token embedding -> the blocks in run order -> final norm on the wanted rows -> output projection
-(src/llmserve/models/transformer.py:125-139, 192-193). The model owns no sizes of its own: they
-all come with the plan's specs.
+(src/llmserve/models/transformer.py:125-139, 192-193). The model owns no sizes or constants of
+its own: they all come with the plan (layer specs, run order, and the optional scale of the
+embedded tokens and scale / soft cap of the logits).
 """
 
 from __future__ import annotations
@@ -69,6 +70,15 @@ class DecoderModel:
             {k[len("final_norm."):]: v for k, v in params.items() if k.startswith("final_norm.")}
         )
 
+    def parts(self):
+        """Every part of the model, blocks and what they are made of."""
+        for block in self.blocks:
+            yield block
+            yield from block.children.values()
+        yield self.final_norm
+        if self.embed_position is not None:
+            yield self.embed_position
+
     # ------------------------------------------------------------------ cache
     def cache_needs(self) -> dict[int, object]:
         """cache id -> what the layer that fills it keeps per request (None: nothing)."""
@@ -101,6 +111,8 @@ class DecoderModel:
     def forward(self, step, pools) -> torch.Tensor:
         """Run this step's tokens; return float32 logits ``[len(step.logit_rows), vocab]``."""
         x = self.ops.embedding(step.token_ids, self.embed_weight)
+        if self.plan.embed_scale != 1.0:
+            x *= self.plan.embed_scale
         if self.embed_position is not None:
             self.embed_position.embed(x, step.positions)  # absolute encodings change x in place
         pending = None
@@ -112,4 +124,10 @@ class DecoderModel:
                 pending.resolve()  # nobody reads x any more, but the kernel set's sums must be taken
             return torch.empty(0, self.plan.vocab_size, dtype=torch.float32, device=x.device)
         h = self.final_norm.forward(x, settle(pending, self.final_norm), rows=step.logit_rows)
-        return self.ops.linear(h, self.head_weight, None, out_dtype=torch.float32)
+        logits = self.ops.linear(h, self.head_weight, None, out_dtype=torch.float32)
+        if self.plan.logit_scale != 1.0:
+            logits *= self.plan.logit_scale
+        if self.plan.logit_softcap > 0.0:
+            cap = self.plan.logit_softcap
+            logits = torch.tanh_(logits.div_(cap)).mul_(cap)
+        return logits

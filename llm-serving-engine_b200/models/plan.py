@@ -29,6 +29,10 @@ class ModelPlan:
     final_norm: Any  # norm spec
     tie_head: bool
     embed_position: Any = None  # position-encoding spec applied to the embedded tokens, or None
+    # constants that some architectures put around the stack of layers (all off by default):
+    embed_scale: float = 1.0  # the embedded tokens are multiplied by this
+    logit_scale: float = 1.0  # the logits are multiplied by this ...
+    logit_softcap: float = 0.0  # ... and then, if > 0, squashed to cap * tanh(logits / cap)
 
     def validate(self) -> None:
         if not self.run_order:

@@ -98,6 +98,10 @@ class StateNeed:
 # --------------------------------------------------------------------------- part base classes
 class Part:
     kind: str = ""
+    # True for a part whose forward reads ``step.host`` (the batch as host arrays) or otherwise
+    # works from the host while the step runs: a model with such a part is never replayed as a
+    # captured CUDA graph, where there is no host step and nothing may synchronise.
+    needs_host_step: bool = False
 
     def __init__(self, spec: Any, env: BuildEnv) -> None:
         self.spec = spec

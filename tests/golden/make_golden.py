@@ -4,17 +4,21 @@ Run from the repository root with the reference checkout available:
 
     python tests/golden/make_golden.py /path/to/reference
 
-It writes a tiny random Llama folder (seeded, via the engine's random-weights mode), loads the same
-tensors into the reference's ``llmserve.models.transformer.CausalLM``, runs the reference's forward
-through its own paged cache with a reversed block table on a fixed token sequence, checks that
-``tests/plain_llama.py`` gives the same logits, and stores the reference's logits in
-``tests/golden/tiny_llama_reference_logits.safetensors`` together with the token ids and a checksum
-of the weights. ``tests/test_plain.py`` replays the comparison from that file without the
-reference.
+For each case it writes a tiny random Llama folder (seeded, via the engine's random-weights mode),
+loads the same tensors into the reference's ``llmserve.models.transformer.CausalLM``, runs the
+reference's forward through its own paged cache with a reversed block table on a fixed token
+sequence, checks that ``tests/plain_llama.py`` gives the same logits, and stores the reference's
+logits in ``tests/golden/tiny_llama_reference_logits.safetensors`` together with the token ids, the
+weights themselves and (in the file's metadata) each case's config.json. ``tests/test_plain.py``
+replays the comparison from that file alone, without the reference and whatever random numbers
+this machine's torch draws. The cases cover grouped and single key/value heads, tied and untied
+heads, attention biases with head size 64, and the "linear" and "llama3" scalings of the rotary
+frequencies (src/llmserve/models/layers.py:24-58, src/llmserve/config.py:47-49,64).
 """
 
 from __future__ import annotations
 
+import json
 import sys
 import tempfile
 from pathlib import Path
@@ -35,6 +39,20 @@ CASES = {
     "mqa_untied": (dict(vocab_size=384, hidden_size=128, intermediate_size=352, num_hidden_layers=3,
                         num_attention_heads=4, num_key_value_heads=1, head_dim=32, rope_theta=100000.0,
                         rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512), 2, 40),
+    "bias_d64": (dict(vocab_size=131, hidden_size=96, intermediate_size=136, num_hidden_layers=1,
+                      num_attention_heads=3, num_key_value_heads=1, head_dim=64, rope_theta=50000.0,
+                      rms_norm_eps=3e-6, tie_word_embeddings=False, attention_bias=True,
+                      max_position_embeddings=128), 7, 50),
+    "rope_linear": (dict(vocab_size=97, hidden_size=48, intermediate_size=80, num_hidden_layers=1,
+                         num_attention_heads=3, num_key_value_heads=3, head_dim=16, rope_theta=10000.0,
+                         rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=256,
+                         rope_scaling={"rope_type": "linear", "factor": 4.0}), 11, 120),
+    "rope_llama3": (dict(vocab_size=97, hidden_size=48, intermediate_size=80, num_hidden_layers=1,
+                         num_attention_heads=3, num_key_value_heads=1, head_dim=32, rope_theta=500000.0,
+                         rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=256,
+                         rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                       "high_freq_factor": 4.0, "original_max_position_embeddings": 64}),
+                    13, 200),
 }
 
 
@@ -48,10 +66,6 @@ def case_inputs(name):
     return cfg, seed, ids
 
 
-def weights_checksum(w: dict[str, torch.Tensor]) -> torch.Tensor:
-    return torch.stack([w[k].double().sum() for k in sorted(w)]).sum().reshape(1)
-
-
 def main(reference_root: str) -> None:
     import plain_llama
     from llmserve_b200.weights import write_random_model
@@ -63,7 +77,7 @@ def main(reference_root: str) -> None:
     from llmserve.models.loader import load_state_dict_into
     from llmserve.models.transformer import CausalLM
 
-    out = {}
+    out, configs = {}, {}
     for name in CASES:
         cfg, seed, ids = case_inputs(name)
         with tempfile.TemporaryDirectory() as d:
@@ -86,8 +100,10 @@ def main(reference_root: str) -> None:
         assert diff < 1e-5, diff
         out[f"{name}.logits"] = logits.contiguous()
         out[f"{name}.ids"] = ids.to(torch.int32)
-        out[f"{name}.checksum"] = weights_checksum(w)
-    save_file(out, str(GOLDEN))
+        for k, v in w.items():
+            out[f"{name}.weights.{k}"] = v.contiguous()
+        configs[name] = cfg.to_dict()
+    save_file(out, str(GOLDEN), metadata={"configs": json.dumps(configs)})
     print("wrote", GOLDEN)
 
 

@@ -10,6 +10,7 @@ import torch
 
 import plain_llama
 import traces
+from conftest import TINY
 
 pytestmark = pytest.mark.gpu
 
@@ -80,6 +81,8 @@ def register_toy():
     @MIXERS.register("toy_decay")
     class DecayMixer(Mixer):
         """s_t = decay * s_{t-1} + x_t W ; y_t = s_t. The state s lives in the request's slot."""
+
+        needs_host_step = True  # the loop below reads the batch on the host: never captured
 
         def param_decls(self):
             h = self.spec.hidden_size
@@ -355,3 +358,88 @@ def test_toy_routed_feed_forward_and_absolute_positions(tiny_dirs):
     expected = {r: plain(t) for r, t in reqs.items()}
     got = traces.replay(runner, traces.mixed(reqs, seed=6))
     traces.compare(got, expected, atol=3e-5)
+
+
+def test_toy_state_mixer_through_the_engine_with_graphs_on(tiny_dirs, tmp_path):
+    """A whole architecture registered from this file alone (its own name in config.json, the toy
+    mixer with state in layer 0) generates through ``LLM`` with CUDA graphs switched on: the toy
+    mixer declares that it works from the host, so no step of this model is captured, and the
+    tokens are the plain model's."""
+    from llmserve_b200 import LLM, LlamaConfig, SamplingParams
+    from llmserve_b200.config.registry import ARCHITECTURES, Architecture, register_architecture
+    from llmserve_b200.models.llama import llama_checkpoint_layout, llama_plan
+    from llmserve_b200.models.plan import ParamSource, Source
+    from llmserve_b200.weights import write_random_model
+
+    register_toy()
+
+    class ToyConfig(LlamaConfig):
+        architecture = "ToyDecayForCausalLM"
+
+    def toy_plan(cfg):
+        plan = llama_plan(cfg)
+        first = dataclasses.replace(plan.layers[0], mixer=DecaySpec(cfg.hidden_size, 0.9))
+        return dataclasses.replace(plan, layers=(first, *plan.layers[1:]))
+
+    def toy_layout(cfg):
+        layout = llama_checkpoint_layout(cfg)
+        keep = tuple(e for e in layout.entries if not e.param.startswith("layers.0.mixer."))
+        mine = ParamSource("layers.0.mixer.w.weight",
+                           (Source("model.layers.0.toy.w.weight", (cfg.hidden_size, cfg.hidden_size)),))
+        return dataclasses.replace(layout, entries=keep + (mine,))
+
+    register_architecture(Architecture("ToyDecayForCausalLM", "toy_decay", ToyConfig, toy_plan, toy_layout))
+    try:
+        base = {k: v for k, v in TINY["A"].items() if k not in ("seed", "page_tokens")}
+        cfg = ToyConfig.from_dict({"model_type": "llama", **base})
+        write_random_model(tmp_path, cfg, seed=3)
+        # sharper weights, so that greedy choices are no near-ties
+        from safetensors.torch import load_file, save_file
+
+        t = {k: (v.float() * 6).to(v.dtype) if v.dim() > 1 else v for k, v in
+             load_file(str(tmp_path / "model.safetensors")).items()}
+        save_file(t, str(tmp_path / "model.safetensors"))
+        llm = LLM(str(tmp_path), dtype="float32", block_size=16, num_kv_blocks=32, max_model_len=256,
+                  max_num_seqs=4, cuda_graphs=True)
+        prompts = [[5, 9, 200, 31, 7], list(range(40, 70)), [3, 4]]
+        outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+        graphs = llm.engine.runner.decode_graphs
+        assert graphs is None or (not graphs.capturable and not graphs.graphs)
+        pcfg, w = plain_llama.read_config(tmp_path), plain_llama.read_weights(tmp_path)
+        mix_w = w["model.layers.0.toy.w.weight"]
+        for p, o in zip(prompts, outs):
+            ids = list(p)
+            for _ in range(10):
+                ids.append(int(toy_plain(w, pcfg, ids, 0.9, mix_w)[-1].argmax()))
+            assert o.outputs[0].token_ids == ids[len(p):]
+    finally:
+        ARCHITECTURES.pop("ToyDecayForCausalLM", None)
+
+
+def test_scales_around_the_stack_of_layers_are_data_of_the_plan(tiny_dirs):
+    """A multiplier on the embedded tokens, a multiplier and a soft cap on the logits: set in the
+    plan, not in the decoder. Compared with the plain model given the scaled embedding table (the
+    head of configuration B is a tensor of its own) and the same two steps on its logits."""
+    from llmserve_b200.config import load_model_config
+    from llmserve_b200.engine.batch import StepEntry
+    from llmserve_b200.engine.runner import ModelRunner
+    from llmserve_b200.models import DecoderModel
+    from llmserve_b200.ops import get_ops
+    from llmserve_b200.parts import BuildEnv
+    from llmserve_b200.weights import load_parameters
+
+    folder = tiny_dirs["B"]
+    arch, cfg = load_model_config(folder)
+    plan = dataclasses.replace(arch.plan(cfg), embed_scale=3.0, logit_scale=0.25, logit_softcap=0.2)
+    ids = traces.make_requests([37], cfg.vocab_size, seed=2)["r0"]
+    w = plain_llama.read_weights(folder)
+    w["model.embed_tokens.weight"] = w["model.embed_tokens.weight"] * 3.0
+    want = plain_llama.forward(plain_llama.read_config(folder), w, ids)
+    want = 0.2 * torch.tanh(want * 0.25 / 0.2)
+    for dtype, bound in ((torch.float32, 1e-5), (torch.bfloat16, 0.03 * float(want.abs().max()))):
+        env = BuildEnv(get_ops("cuda"), dtype, torch.device("cuda"), 512, torch.float32)
+        model = DecoderModel(plan, env)
+        model.bind(load_parameters(folder, arch.checkpoint_layout(cfg), dtype, "cuda"))
+        runner = ModelRunner(model, page_tokens=8, num_pages=8, max_model_len=512, max_num_seqs=2)
+        got = runner.run([StepEntry("r", ids, list(range(len(ids))))]).float().cpu()
+        assert (got - want).abs().max() <= bound

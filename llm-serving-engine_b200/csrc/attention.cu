@@ -945,6 +945,30 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   const T* vp = (const T*)a.v_pages;
   const bool page_holds_tile = page_shift >= 4;  // pages of 16, 32, ... tokens: a tile of 16 aligned keys lies in one
 
+  // Keys and values of earlier steps do not depend on the kernels before this one in the stream
+  // (those write this step's row only), and neither do the block tables. So before the
+  // dependency wait the rows of this warp's first two tiles are asked into L2 (one row of K or V
+  // per lane; no registers are held across the wait), unless the tile holds this step's key.
+  auto row_base = [&](int key) -> size_t {
+    int pi, off;
+    page_of(key, a.page_tokens, page_shift, pi, off);
+    return (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
+  };
+  auto inside = [&](int key) { return min(max(key, lo), hi - 1); };  // masked keys read a valid row
+  const int first_tile = lo >> 4, last_tile = (hi - 1) >> 4;
+  if (hi > lo) {
+#pragma unroll
+    for (int ahead = 0; ahead < 2; ++ahead) {
+      const int tile = first_tile + warp + ahead * DEC_WARPS;
+      if (tile <= last_tile && tile * 16 + 16 <= ctx - 1) {
+        const T* row = (lane < 16 ? kp : vp) + row_base(inside(tile * 16 + (lane & 15)));
+#pragma unroll
+        for (int b = 0; b < D * (int)sizeof(T); b += 128)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(row) + b));
+      }
+    }
+  }
+
   pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
 
   // Q^T as the column operand: column g is head h0 + g (zero beyond the group); multiply step s
@@ -968,14 +992,7 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   for (int i = 0; i < MT; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2t and 2t + 1
 
-  auto row_base = [&](int key) -> size_t {
-    int pi, off;
-    page_of(key, a.page_tokens, page_shift, pi, off);
-    return (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
-  };
-  auto inside = [&](int key) { return min(max(key, lo), hi - 1); };  // masked keys read a valid row
   if (hi > lo) {
-    const int first_tile = lo >> 4, last_tile = (hi - 1) >> 4;
     for (int tile = first_tile + warp; tile <= last_tile; tile += DEC_WARPS) {
       const int j0 = tile * 16;
       size_t kb[2], vb[4];

@@ -914,6 +914,9 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
+// EARLY: the rows of the warp's first tile are loaded into registers before the dependency wait
+// (the registers stay live across it, which costs occupancy: for grids that do not fill the SMs).
+template <bool EARLY>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   using T = bf16;
@@ -947,20 +950,55 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
 
   // Keys and values of earlier steps do not depend on the kernels before this one in the stream
   // (those write this step's row only), and neither do the block tables. So before the
-  // dependency wait the rows of this warp's first two tiles are asked into L2 (one row of K or V
-  // per lane; no registers are held across the wait), unless the tile holds this step's key.
+  // dependency wait the rows of this warp's first tiles are asked for, unless a tile holds this
+  // step's key: into L2 (one row of K or V per lane, no registers held across the wait), or, in
+  // the EARLY kernel, the first tile straight into the operand registers.
   auto row_base = [&](int key) -> size_t {
     int pi, off;
     page_of(key, a.page_tokens, page_shift, pi, off);
     return (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
   };
   auto inside = [&](int key) { return min(max(key, lo), hi - 1); };  // masked keys read a valid row
+  uint4 kr[2][KCH], vr[4][VCH];
+  auto fetch = [&](int tile) {  // the tile's rows into operand registers
+    const int j0 = tile * 16;
+    size_t kb[2], vb[4];
+    if (page_holds_tile) {
+      const size_t page_row = ((size_t)table[j0 >> page_shift] * a.num_kv_heads + kvh) * a.page_tokens;
+      const int mask = a.page_tokens - 1;
+      kb[0] = (page_row + (inside(j0 + g) & mask)) * D;
+      kb[1] = (page_row + (inside(j0 + g + 8) & mask)) * D;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        vb[i] = (page_row + (inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)) & mask)) * D;
+    } else {
+      kb[0] = row_base(inside(j0 + g));
+      kb[1] = row_base(inside(j0 + g + 8));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) vb[i] = row_base(inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int c = 0; c < KCH; ++c)
+        kr[r][c] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * (t + 4 * c));
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < VCH; ++c)
+        vr[i][c] = *reinterpret_cast<const uint4*>(vp + vb[i] + 8 * (g + 8 * c));
+  };
   const int first_tile = lo >> 4, last_tile = (hi - 1) >> 4;
-  if (hi > lo) {
+  auto older = [&](int tile) { return hi > lo && tile <= last_tile && tile * 16 + 16 <= ctx - 1; };
+  bool fetched = false;
+  if (EARLY) {
+    fetched = older(first_tile + warp);
+    if (fetched) fetch(first_tile + warp);
+  } else {
 #pragma unroll
     for (int ahead = 0; ahead < 2; ++ahead) {
       const int tile = first_tile + warp + ahead * DEC_WARPS;
-      if (tile <= last_tile && tile * 16 + 16 <= ctx - 1) {
+      if (older(tile)) {
         const T* row = (lane < 16 ? kp : vp) + row_base(inside(tile * 16 + (lane & 15)));
 #pragma unroll
         for (int b = 0; b < D * (int)sizeof(T); b += 128)
@@ -995,32 +1033,8 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   if (hi > lo) {
     for (int tile = first_tile + warp; tile <= last_tile; tile += DEC_WARPS) {
       const int j0 = tile * 16;
-      size_t kb[2], vb[4];
-      if (page_holds_tile) {
-        const size_t page_row = ((size_t)table[j0 >> page_shift] * a.num_kv_heads + kvh) * a.page_tokens;
-        const int mask = a.page_tokens - 1;
-        kb[0] = (page_row + (inside(j0 + g) & mask)) * D;
-        kb[1] = (page_row + (inside(j0 + g + 8) & mask)) * D;
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          vb[i] = (page_row + (inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)) & mask)) * D;
-      } else {
-        kb[0] = row_base(inside(j0 + g));
-        kb[1] = row_base(inside(j0 + g + 8));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) vb[i] = row_base(inside(j0 + 2 * t + (i & 1) + 8 * (i >> 1)));
-      }
-      uint4 kr[2][KCH], vr[4][VCH];
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int c = 0; c < KCH; ++c)
-          kr[r][c] = *reinterpret_cast<const uint4*>(kp + kb[r] + 8 * (t + 4 * c));
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < VCH; ++c)
-          vr[i][c] = *reinterpret_cast<const uint4*>(vp + vb[i] + 8 * (g + 8 * c));
+      if (!fetched) fetch(tile);
+      fetched = false;
 
       // S^T[keys g, g + 8][heads 2t, 2t+1]
       float sc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1167,7 +1181,18 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     if (mgrid.y > 65535 || mgrid.z > 65535) return LSE_BAD_ARGUMENT;
     if (a->num_splits > 1 && (size_t)mgrid.y * mgrid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
     if (a->num_splits > MERGE_SPLITS) return LSE_BAD_ARGUMENT;
-    if (G <= 8) launch(decode_mma8_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+    if (G <= 8) {
+      // a grid that leaves the SMs part empty can afford the registers of an early first tile
+      static int sms = 0;
+      if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      }
+      const bool small = (long long)mgrid.x * mgrid.y * mgrid.z <= 4LL * sms;
+      if (small) launch(decode_mma8_kernel<true>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+      else launch(decode_mma8_kernel<false>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+    }
 #if LSE_HEAD_DIM == 64
     else launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
 #endif

@@ -917,7 +917,7 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // EARLY: the rows of the warp's first tile are loaded into registers before the dependency wait
 // (the registers stay live across it, which costs occupancy: for grids that do not fill the SMs).
 template <bool EARLY>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__global__ void __launch_bounds__(DEC_WARPS * 32, EARLY ? 4 : 0)  // 0: no promise, the compiler's own choice
 decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   using T = bf16;
   constexpr int HEADS = 8;

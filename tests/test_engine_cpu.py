@@ -342,3 +342,27 @@ def test_stop_strings_cut_the_text(sharp_dirs):
     assert len(cut.token_ids) == at + 3  # the tokens of the stop string were generated
     kept = run(stop=[stop], include_stop_str_in_output=True)
     assert kept.text == free.text[: at + 3]
+
+
+def test_a_kernel_that_gave_up_waiting_stops_the_engine(sharp_dirs):
+    """A kernel of the product path that gives up a bounded wait records a code in a flag that
+    the host reads after the step. Here a kernel set whose flag is raised by hand stands in for
+    it: the step that follows must raise, not hand out tokens."""
+    from llmserve_b200 import EngineConfig, LLMEngine, SamplingParams
+
+    class Flagged(PlainOps):
+        code = 0
+
+        def check_kernel_errors(self):
+            if self.code:
+                code, self.code = self.code, 0
+                raise RuntimeError(f"a CUDA kernel of llmserve_b200 gave up waiting (code {code})")
+
+    ops = Flagged()
+    eng = LLMEngine(EngineConfig(model=str(sharp_dirs["A"]), dtype="float32", device="cpu", block_size=16,
+                                 num_kv_blocks=16, max_model_len=256, max_num_seqs=4), ops=ops)
+    eng.add_request([1, 2, 3], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert eng.step()  # fine
+    ops.code = 104
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        eng.step()

@@ -4,12 +4,14 @@ from __future__ import annotations
 
 from conftest import TINY
 
-# Tolerances, fixed before the first GPU run.
+# Tolerances.
 #   float32: the engine and the plain model differ only in the order of float32 additions.
 #   bfloat16: activations are rounded to 8 bits of mantissa between kernels (about 6 roundings per
-#   layer); the bound is 3 % of the largest logit of the compared requests.
+#   layer); the bound is 2 % of the largest logit of the compared requests. (It was 3 % before the
+#   first GPU run; measured since: at most 0.8 % on the tiny configurations, 0.9 % at SmolLM2-1.7B
+#   layer widths, 1.5 % with the sharpened attention of tests/test_gpu_widths.py, so it was tightened.)
 F32_ATOL = 2e-5
-BF16_RTOL = 0.03
+BF16_RTOL = 0.02
 
 
 def tolerances(dtype):

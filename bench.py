@@ -139,10 +139,11 @@ def make_engine(args, layers_full: int):
 
     over = {"num_hidden_layers": args.layers} if args.layers != layers_full else None
     max_b = max(64, args.batch)
-    tokens_per_req = -(-(PROMPT_LEN + 2 * (args.steps + args.warmup) + 64) // 16) * 16
+    page = args.page_tokens
+    tokens_per_req = -(-(PROMPT_LEN + 2 * (args.steps + args.warmup) + 64) // page) * page
     return LLMEngine(EngineConfig(
-        model=f"random:{args.model}", dtype="bfloat16", seed=4, block_size=16,
-        num_kv_blocks=max_b * tokens_per_req // 16, max_model_len=CONTEXT, max_num_seqs=max_b,
+        model=f"random:{args.model}", dtype="bfloat16", seed=4, block_size=page,
+        num_kv_blocks=max_b * tokens_per_req // page, max_model_len=CONTEXT, max_num_seqs=max_b,
         max_num_batched_tokens=PREFILL_TOKENS, config_overrides=over))
 
 
@@ -311,7 +312,7 @@ def decode_main(args) -> int:
             "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
             "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
             "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
-            "decode_ctx": main_pt["ctx"], "page_tokens": 16, "parallelism": "single-gpu",
+            "decode_ctx": main_pt["ctx"], "page_tokens": args.page_tokens, "parallelism": "single-gpu",
             "cuda_graphs": True, "l2": "inputs larger than L2 (weights + cache streamed each step)",
             "peaks": pk["source"],
         },
@@ -611,6 +612,7 @@ def reference_main(args) -> int:
 
 
 def main() -> int:
+    global PROMPT_LEN, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -623,9 +625,15 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill points")
     ap.add_argument("--parity", action="store_true",
                     help="also compare a two-layer model of the same layer sizes with the plain implementation")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                    help="prompt length of the decode workload (the context grows from there)")
+    ap.add_argument("--page-tokens", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--parity-layers", type=int, default=0,
                     help="layers of the float32 replay of --workload long (0 = all)")
     args = ap.parse_args()
+    if args.prompt_len != PROMPT_LEN:  # another point of the same workload: longer or shorter contexts
+        PROMPT_LEN = args.prompt_len
+        CONTEXT = max(CONTEXT, -(-(PROMPT_LEN + 2 * (args.steps + args.warmup) + 128) // 1024) * 1024)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print("bench.py: this engine runs on one GPU; --gpus > 1 is not built")
         return 2

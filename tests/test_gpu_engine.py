@@ -258,6 +258,27 @@ def test_running_ahead_changes_nothing(sharp_dirs, dtype):
     assert [len(t) for t, _ in outs[True]][1:] == [17, 25, 30]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_that_are_never_cut(sharp_dirs, dtype):
+    """``enable_chunked_prefill=False`` on the GPU: a prompt longer than the budget runs in a step
+    of its own while the others pause; float32 tokens are the plain model's, bfloat16 tokens the
+    same on two runs."""
+    import numpy as np
+
+    rng = np.random.default_rng(9)
+    v = TINY["C"]["vocab_size"]
+    prompts = [rng.integers(0, v, n).tolist() for n in (5, 70, 12, 33)]
+    runs = []
+    for _ in range(2):
+        m = llm(sharp_dirs["C"], "C", dtype, enable_chunked_prefill=False, max_num_batched_tokens=40)
+        runs.append([o.outputs[0].token_ids for o in m.generate(prompts, greedy(9))])
+        m.engine.manager.check_invariants()
+        assert m.engine.manager.usage() == 0.0
+    assert runs[0] == runs[1]
+    if dtype == "float32":
+        assert runs[0] == [plain_llama.greedy(sharp_dirs["C"], p, 9) for p in prompts]
+
+
 def test_abort_while_a_step_is_in_flight(sharp_dirs):
     from llmserve_b200 import SamplingParams
 

@@ -85,6 +85,7 @@ def test_gemm_f32_is_true_float32_and_batch_invariant(ops, T, N, K, bias):
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 48, 64), (9, 520, 200), (16, 128, 64), (17, 2048, 2048),
+                                   (8, 16384, 2048), (4, 49152, 2048), (8, 6144, 2048), (2, 2048, 8192),
                                    (64, 136, 1000), (100, 384, 8192), (256, 1000, 520), (300, 136, 1000)])
 @pytest.mark.parametrize("bias", [False, True])
 def test_linear_bf16(ops, T, N, K, bias):
@@ -336,6 +337,18 @@ def test_decode_on_tensor_core_tiles(ops, nq, nk, D, page, window):
     for splits in (1, 4):
         got, ref, _ = run_attention(ops, case, nq, nk, D, page, window, 512, splits=splits)
         close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
+
+
+@pytest.mark.parametrize("batch,ctx,nq,nk", [(64, 2100, 8, 8), (64, 2100, 6, 2), (1, 2300, 32, 32), (40, 4100, 4, 2)])
+def test_decode_over_long_contexts_at_large_batch(ops, batch, ctx, nq, nk):
+    """The benchmark's decode shapes: 64 sequences of more than 2000 keys each (one partition per
+    sequence), one sequence of 2300 keys (17 partitions, the variant that loads its first tile
+    early), 40 sequences of 4100. All context lengths differ, pages are shuffled."""
+    D, page = 64, 16
+    ctx_lens = [ctx - 7 * i % 97 for i in range(batch)]
+    case = paged_case(batch, [1] * batch, ctx_lens, nq, nk, D, page, torch.bfloat16, seed=batch)
+    got, ref, _ = run_attention(ops, case, nq, nk, D, page, 0, 4200)
+    close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
 
 
 @pytest.mark.parametrize("group", [3, 8, 12])

@@ -8,7 +8,8 @@
 // the normaliser and the weighted sum are float32 (src/llmserve/kernels/csrc/
 // paged_attention.cpp:191-243 does the same on the CPU). Keys and values are read from pages
 // [page][kv_head][offset][D] through the sequence's block table; nothing at or beyond a sequence's
-// context length is ever read, so pages that another request used before need no clearing.
+// context length is ever used (the TMA-fed kernel copies whole tiles of 16 rows and masks or zeroes
+// the rows it may not use), so pages that another request used before need no clearing.
 //
 // Kernels:
 //   prefill_simt  portions of >= 2 rows, any dtype: 32 rows per block, 4 threads per row.
@@ -27,11 +28,14 @@
 //   decode_mma8 / decode_mma  single rows, bfloat16: the same partitions and merge with mma.sync
 //                 tensor-core tiles: keys x heads for up to 8 heads per key/value head (head
 //                 sizes 64 and 128), heads x keys for 9 to 16 (head size 64).
+//   decode_ring   decode_mma8 with its key/value tiles brought by TMA into swizzled shared memory
+//                 (pages of 16 tokens or more): for grids of many waves.
 #include <type_traits>
 
 #include "attention_args.h"
 #include "common.cuh"
 #include "kernels.h"
+#include "tma_util.cuh"
 #if LSE_HEAD_DIM == 64
 #include "attention_tc.cuh"
 #endif
@@ -1148,6 +1152,276 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
 }
+
+// The same computation fed by TMA: every warp has PER slots of 128-byte-swizzled shared memory, each
+// for one key/value tile (16 keys), and asks for its next tile as soon as a slot's contents are in
+// its registers (ldmatrix), so a tile's load runs while the tile before it is worked on. Tiles of
+// earlier steps are asked for before the dependency wait. A tile is 16 consecutive rows of one
+// page, so this kernel needs pages of at least 16 tokens; a tile's rows outside the partition
+// (other partitions' keys, or rows of the page that were never written) are masked out of the
+// scores and zeroed as values before they are used. (A separate producer warp with a ring of 8 or
+// 12 tiles per block was slower: 178 us against 159 at batch 64, 37.7 against 30.5 at batch 8; the
+// hand-over between warps costs more than the deeper ring gains.)
+namespace ring {
+using namespace tma;
+constexpr int BOXES = D / 64;             // TMA boxes of 64 head dims per row
+constexpr int TILE_BYTES = 16 * D * 2;    // keys or values of one tile
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// byte offset of 16-byte piece `c` (8 head dims) of row `r` inside a tile: box c / 8 holds pieces
+// 8 (c / 8) .. + 7 of all 16 rows, rows of 128 bytes, pieces permuted by the 128-byte swizzle
+__device__ __forceinline__ uint32_t piece(int r, int c) {
+  return (uint32_t)((c >> 3) * 2048 + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+}  // namespace ring
+
+// PER: tiles in flight per warp. Every warp is its own producer: lane 0 asks for the warp's tile
+// k + PER into the slot that tile k has just been read from, so no warp waits for another.
+template <int PER>
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+decode_ring_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                   const LseAttnArgs a, int page_shift) {
+  using T = bf16;
+  using namespace ring;
+  constexpr int HEADS = 8;
+  constexpr int KS = D / 16;   // multiply steps of K Q^T
+  constexpr int MT = D / 16;   // output tiles of 16 head dims
+  constexpr int SLOTS = PER * DEC_WARPS;
+  extern __shared__ __align__(1024) unsigned char ring_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(ring_raw) + 1023) & ~(uintptr_t)1023);  // [SLOTS][K tile, V tile]
+  __shared__ __align__(8) uint64_t full[SLOTS];
+  __shared__ float sm_m[DEC_WARPS][HEADS], sm_l[DEC_WARPS][HEADS];
+  __shared__ float sm_acc[DEC_WARPS][HEADS][D];
+  __shared__ volatile int failed;
+  pdl_trigger();
+
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int G = a.num_heads / a.num_kv_heads;
+  const int h0 = kvh * G;
+  const int seq = a.decode_seqs[b];
+  const int tok = a.cu_q[seq];
+  const int ctx = a.ctx_lens[seq];
+  const int k_first = a.window > 0 ? max(0, ctx - a.window) : 0;
+  const int span = ctx - k_first;
+  const int per = (span + a.num_splits - 1) / a.num_splits;
+  const int lo = k_first + split * per;
+  const int hi = min(ctx, lo + per);
+  const int first_tile = lo >> 4;
+  const int n_tiles = hi > lo ? ((hi - 1) >> 4) - first_tile + 1 : 0;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n_mine = n_tiles > warp ? (n_tiles - warp + DEC_WARPS - 1) / DEC_WARPS : 0;  // tiles warp, warp + 4, ...
+  if (threadIdx.x == 0) {
+    failed = 0;
+    for (int s = 0; s < SLOTS; ++s) mbar_init(&full[s], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  __syncthreads();
+
+  const int* table = a.block_tables + (size_t)seq * a.table_stride;
+  const int mask = a.page_tokens - 1;
+  // rows of the warp's tiles base .. base + 31 (of its own count), one per lane: one dependent
+  // load for 32 tiles instead of one per tile
+  int rows_base = 0, my_row = 0;
+  auto look_up = [&](int base) {
+    rows_base = base;
+    my_row = 0;
+    if (base + lane < n_mine) {
+      const int j0 = (first_tile + warp + (base + lane) * DEC_WARPS) * 16;
+      my_row = (int)(((long long)table[j0 >> page_shift] * a.num_kv_heads + kvh) * a.page_tokens + (j0 & mask));
+    }
+  };
+  auto ask = [&](int k) {  // all lanes call; lane 0 asks
+    if (k >= rows_base + 32) look_up(k);
+    const int row = __shfl_sync(0xffffffffu, my_row, k - rows_base);
+    if (lane == 0) {
+      const int s = warp * PER + k % PER;
+      unsigned char* kt = tiles + (size_t)s * 2 * TILE_BYTES;
+      mbar_expect_tx(&full[s], 2 * TILE_BYTES);
+#pragma unroll
+      for (int x = 0; x < BOXES; ++x) {
+        tma_load_2d(kt + x * 2048, &map_k, &full[s], x * 64, row);
+        tma_load_2d(kt + TILE_BYTES + x * 2048, &map_v, &full[s], x * 64, row);
+      }
+    }
+  };
+  // Keys and values of earlier steps depend on no kernel before this one in the stream (those
+  // write this step's row only), and neither do the block tables: tiles of earlier steps are
+  // asked for before the dependency wait.
+  look_up(0);
+  int asked = 0;
+  for (; asked < n_mine && asked < PER && (first_tile + warp + asked * DEC_WARPS) * 16 + 16 <= ctx - 1; ++asked)
+    ask(asked);
+  pdl_wait();  // queries and this step's key/value row come from the kernels before this one
+  for (; asked < n_mine && asked < PER; ++asked) ask(asked);
+
+  // Q^T as the column operand of step s: heads g, head dims 16 s + 2t, +1 and + 8, + 9
+  uint32_t qb[KS][2];
+#pragma unroll
+  for (int s = 0; s < KS; ++s) {
+    qb[s][0] = qb[s][1] = 0;
+    if (g < G) {
+      const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + g) * D + 16 * s + 2 * t;
+      qb[s][0] = *reinterpret_cast<const uint32_t*>(q);
+      qb[s][1] = *reinterpret_cast<const uint32_t*>(q + 8);
+    }
+  }
+  float ot[MT][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i) ot[i][0] = ot[i][1] = ot[i][2] = ot[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};  // heads 2t and 2t + 1
+
+  const int mat = lane >> 3, r8 = lane & 7;
+  int k = 0;
+  for (; k < n_mine; ++k) {
+    const int s = warp * PER + k % PER, j0 = (first_tile + warp + k * DEC_WARPS) * 16;
+    if (!mbar_wait(&full[s], (k / PER) & 1)) {
+      failed = 2;
+      break;
+    }
+    unsigned char* kt = tiles + (size_t)s * 2 * TILE_BYTES;
+    unsigned char* vt = kt + TILE_BYTES;
+    if (j0 < lo || j0 + 16 > hi) {
+      // rows outside the partition may hold anything (also NaN bits in rows never written):
+      // zero them as values, so that their weight of zero gives zero
+      const int r = lane >> 1;
+      if (j0 + r < lo || j0 + r >= hi) {
+#pragma unroll
+        for (int x = 0; x < BOXES; ++x) {
+          uint4* row = reinterpret_cast<uint4*>(vt + x * 2048 + r * 128 + (lane & 1) * 64);
+          row[0] = row[1] = row[2] = row[3] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      __syncwarp();
+    }
+    const uint32_t kaddr = smem_u32(kt), vaddr = smem_u32(vt);
+    // S^T[keys g, g + 8][heads 2t, 2t+1]
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      uint32_t ka[4];  // keys 0-7 / 8-15 (mat & 1), pieces 2 ks / 2 ks + 1 (mat >> 1)
+      ldmatrix_x4(ka, kaddr + piece((mat & 1) * 8 + r8, 2 * ks + (mat >> 1)));
+      mma_bf16(sc, ka, qb[ks][0], qb[ks][1]);
+    }
+    uint32_t va[MT][4];  // V^T: head dims 16 m .. + 7 / + 8 .. + 15 (mat & 1), keys 0-7 / 8-15 (mat >> 1)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) ldmatrix_x4_trans(va[m], vaddr + piece((mat >> 1) * 8 + r8, 2 * m + (mat & 1)));
+    // the tile is in registers: its slot can take the warp's tile k + PER
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (k + PER < n_mine) ask(k + PER);
+
+    const bool ok0 = j0 + g >= lo && j0 + g < hi, ok1 = j0 + g + 8 >= lo && j0 + g + 8 < hi;
+    float corr[2], p[2][2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float s0 = ok0 ? sc[e] * a.scale : -INFINITY;
+      const float s1 = ok1 ? sc[2 + e] * a.scale : -INFINITY;
+      float mx = fmaxf(m_run[e], fmaxf(s0, s1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      const float m_fin = (mx == -INFINITY) ? 0.f : mx;
+      corr[e] = Exp<T>::f(m_run[e] - m_fin);
+      m_run[e] = mx;
+      p[e][0] = Exp<T>::f(s0 - m_fin);
+      p[e][1] = Exp<T>::f(s1 - m_fin);
+      l_run[e] = l_run[e] * corr[e] + p[e][0] + p[e][1];  // this thread's share; joined at the end
+    }
+    // P^T[keys 2t, 2t+1 / 2t+8, 2t+9][head g] from P[key g / g + 8][heads 2t, 2t+1]
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(p[0][0], p[1][0]));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16(p[0][1], p[1][1]));
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      ot[m][0] *= corr[0];
+      ot[m][1] *= corr[1];
+      ot[m][2] *= corr[0];
+      ot[m][3] *= corr[1];
+      mma_bf16(ot[m], va[m], pb0, pb1);
+    }
+  }
+  if (k < n_mine) {
+    // a wait ran out: the tiles still asked for must land before the block's memory is given up
+    for (int c = k; c < n_mine && c < k + PER; ++c)
+      if (!mbar_wait(&full[warp * PER + c % PER], (c / PER) & 1)) break;
+  }
+  // this warp's result in shared memory
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    float l = l_run[e];
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    const int head = 2 * t + e;
+    if (head < G) {
+      if (g == 0) {
+        sm_m[warp][head] = m_run[e];
+        sm_l[warp][head] = l;
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        sm_acc[warp][head][16 * m + g] = ot[m][e];
+        sm_acc[warp][head][16 * m + g + 8] = ot[m][2 + e];
+      }
+    }
+  }
+  __syncthreads();
+  if (failed && threadIdx.x == 0 && a.error_flag) atomicExch(a.error_flag, 200 + failed);
+  // merge the warps; one thread per (head, dim)
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int gq = idx / D, d = idx - gq * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, sm_m[w][gq]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_WARPS; ++w) {
+      const float wt = (sm_m[w][gq] == -INFINITY) ? 0.f : Exp<T>::f(sm_m[w][gq] - M);
+      L += sm_l[w][gq] * wt;
+      A += sm_acc[w][gq][d] * wt;
+    }
+    const int h = h0 + gq;
+    if (a.num_splits == 1) {
+      T* op = (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h * D;
+      op[d] = Num<T>::from_float(L > 0.f ? A / L : 0.f);
+    } else {
+      float* part = a.scratch + LSE_ATTN_COUNTERS +
+                    (((size_t)b * a.num_heads + h) * a.num_splits + split) * (D + 2);
+      part[d] = A;
+      if (d == 0) {
+        part[D] = M;
+        part[D + 1] = L;
+      }
+    }
+  }
+  if (a.num_splits == 1) return;
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = reinterpret_cast<int*>(a.scratch) + (size_t)b * gridDim.y + blockIdx.y;
+    const int done = atomicAdd(counter, 1);
+    is_last = (done == a.num_splits - 1);
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  merge_partitions<T, HEADS>(
+      a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
+      a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
+}
 #else
 constexpr bool kHasDecodeMma8 = false;
 #endif  // LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
@@ -1176,20 +1450,45 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
   // still issues fewer instructions per key than a dot product on the CUDA cores (head size 64,
   // batch 8, 2176 keys: 27.1 us against 30.6; batch 64: 168 against 176).
   constexpr int kMmaHeads = LSE_HEAD_DIM == 64 ? 16 : 8;  // 9..16 heads: head size 64 only
-  if (std::is_same<T, bf16>::value && G <= kMmaHeads && a->force_simt == 0) {
+  if (std::is_same<T, bf16>::value && G <= kMmaHeads && a->force_simt != 1) {
     dim3 mgrid(a->num_splits, a->num_kv_heads, a->num_decode);
     if (mgrid.y > 65535 || mgrid.z > 65535) return LSE_BAD_ARGUMENT;
     if (a->num_splits > 1 && (size_t)mgrid.y * mgrid.z > (size_t)LSE_ATTN_COUNTERS) return LSE_BAD_ARGUMENT;
     if (a->num_splits > MERGE_SPLITS) return LSE_BAD_ARGUMENT;
+    static int sms = 0;
+    if (!sms) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const long long blocks = (long long)mgrid.x * mgrid.y * mgrid.z;
+    const long long pool_rows = a->num_pages * a->num_kv_heads * a->page_tokens;
+    // The TMA-fed kernel needs pages that hold whole tiles of 16 keys and the pool's size. It is
+    // the faster one for grids of many waves (head size 64, 2118 keys, alone: batch 64 159 us
+    // against 164, batch 48 133 against 143; in the whole step batch 64 gains 2.7 %), the
+    // register-fed one for grids of about one wave (batch 8: 27.3 us against 30.6; batch 32: 86
+    // against 89), where a block's start (barriers, descriptor fetch) is a larger share.
+    const bool ring_can = G <= 8 && ps >= 4 && pool_rows > 0 && pool_rows < (1LL << 31);
+    if (ring_can && (a->force_simt == 3 || (a->force_simt == 0 && blocks >= 10LL * sms))) {
+      constexpr int PER = 1;
+      constexpr int smem = PER * DEC_WARPS * 2 * ring::TILE_BYTES + 1024;
+      static bool configured = false;
+      if (!configured) {
+        if (cudaFuncSetAttribute(decode_ring_kernel<PER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem) != cudaSuccess)
+          return LSE_LAUNCH_FAILED;
+        configured = true;
+      }
+      CUtensorMap mk, mv;
+      if (!tma::make_map_bf16(&mk, a->k_pages, pool_rows, D, D, 16) ||
+          !tma::make_map_bf16(&mv, a->v_pages, pool_rows, D, D, 16))
+        return LSE_LAUNCH_FAILED;
+      launch(decode_ring_kernel<PER>, mgrid, DEC_WARPS * 32, smem, stream, mk, mv, *a, ps);
+      return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
+    }
     if (G <= 8) {
       // a grid that leaves the SMs part empty can afford the registers of an early first tile
-      static int sms = 0;
-      if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-      }
-      const bool small = (long long)mgrid.x * mgrid.y * mgrid.z <= 4LL * sms;
+      const bool small = blocks <= 4LL * sms;
       if (small) launch(decode_mma8_kernel<true>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
       else launch(decode_mma8_kernel<false>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
     }

@@ -28,7 +28,9 @@ struct LseAttnArgs {
   const int* tiles;        // [num_tiles, 2]: sequence, first row of the tile within its portion
   int num_tiles;
   int force_simt;          // 0: fastest kernel that serves the arguments; 1: the CUDA-core kernel;
-                           // 2: the mma.sync tensor-core kernel (no tcgen05)
+                           // 2: the mma.sync tensor-core kernel fed by plain loads (no tcgen05, no
+                           // TMA); 3: single tokens on the TMA-fed kernel whatever the grid's size
+                           // (portions as with 2)
   // single tokens
   const int* decode_seqs;  // [num_decode] sequence indices with one row each
   int num_decode;

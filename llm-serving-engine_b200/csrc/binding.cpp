@@ -18,11 +18,17 @@ namespace {
 using torch::Tensor;
 using OptTensor = std::optional<Tensor>;
 
+// Numbers go into messages as strings made here: streaming an integer or a double into an error
+// message (operator<< of an ostream) has crashed the interpreter in builds of this extension on
+// some hosts, and an error path must never do that.
+template <typename N>
+std::string num(N v) { return std::to_string(v); }
+
 int dtype_code(const Tensor& t, const char* what) {
   if (t.scalar_type() == torch::kFloat32) return LSE_F32;
   if (t.scalar_type() == torch::kBFloat16) return LSE_BF16;
   if (t.scalar_type() == torch::kInt64) return LSE_FIXED64;  // fixed-point sums of the few-rows product
-  TORCH_CHECK(false, what, ": dtype must be float32 or bfloat16, got ", t.scalar_type());
+  TORCH_CHECK(false, what, ": dtype must be float32 or bfloat16, got ", c10::toString(t.scalar_type()));
 }
 
 void check_cuda(const Tensor& t, const char* what) {
@@ -94,7 +100,7 @@ void add_rmsnorm(Tensor& x, const OptTensor& residual, const Tensor& weight, dou
     rows_ptr = rows->data_ptr<int>();
     T = (int)rows->size(0);
   }
-  TORCH_CHECK(out.size(0) == T, "add_rmsnorm: out has ", out.size(0), " rows, expected ", T);
+  TORCH_CHECK(out.size(0) == T, "add_rmsnorm: out has ", num(out.size(0)), " rows, expected ", num(T));
   done(lse_add_rmsnorm(x.data_ptr<float>(), rptr, rcode, weight.data_ptr<float>(), (float)eps,
                        out.data_ptr(), dtype_code(out, "out"), rows_ptr, T, H, stream()),
        "add_rmsnorm");
@@ -260,13 +266,13 @@ void load_attention_library(const std::string& path, int64_t head_dim) {
   TORCH_CHECK(lib.head_dim && lib.q_tile && lib.scratch_floats && lib.prefill && lib.decode,
               "attention library ", path, " lacks an entry point");
   TORCH_CHECK(lib.head_dim() == head_dim, "attention library ", path, " was built for head size ",
-              lib.head_dim(), ", not ", head_dim);
+              num(lib.head_dim()), ", not ", num(head_dim));
   libs()[(int)head_dim] = lib;
 }
 
 const AttnLib& attn_lib(int64_t D) {
   auto it = libs().find((int)D);
-  TORCH_CHECK(it != libs().end(), "no attention library loaded for head size ", D);
+  TORCH_CHECK(it != libs().end(), "no attention library loaded for head size ", num(D));
   return it->second;
 }
 

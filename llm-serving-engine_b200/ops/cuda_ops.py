@@ -68,7 +68,8 @@ class CudaOps:
         self._sample_scratch: torch.Tensor | None = None
         self._sample_rows = 0
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-        self.attention_kernel = 0  # 0: fastest available; 1: CUDA cores; 2: mma.sync (tests compare them)
+        # 0: fastest available; 1: CUDA cores; 2: mma.sync fed by plain loads; 3: single tokens fed by TMA
+        self.attention_kernel = 0  # (tests compare them)
         self.use_skinny_gemm = True
         # rows up to which the own tcgen05 product runs (measured: above it the library is faster)
         self.skinny_max_rows = int(self.ext.gemm_bf16_skinny_max_rows())

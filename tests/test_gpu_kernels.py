@@ -351,8 +351,56 @@ def test_decode_over_long_contexts_at_large_batch(ops, batch, ctx, nq, nk):
     close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
 
 
+@pytest.mark.parametrize("window", [0, 75])
+@pytest.mark.parametrize("nq,nk,D,page", [(4, 4, 64, 16), (8, 1, 64, 64), (6, 2, 64, 32), (8, 2, 128, 16), (3, 3, 128, 128)])
+def test_the_three_decode_kernels_agree(ops, nq, nk, D, page, window):
+    """Single tokens on the CUDA cores, on mma.sync fed by plain loads, and on mma.sync fed by TMA
+    (forced: alone it serves large grids only): ragged contexts from 1 key to several partitions,
+    shuffled pages whose unused rows hold huge values, one and several partitions."""
+    ctx_lens = [1, 15, 16, 17, 33, 130, 513, 700, 64, 129]
+    n = len(ctx_lens)
+    case = paged_case(n, [1] * n, ctx_lens, nq, nk, D, page, torch.bfloat16, seed=nq + D)
+    outs = {}
+    try:
+        for kernel in (1, 2, 3):
+            ops.attention_kernel = kernel
+            for splits in (1, 3, 7):
+                got, ref, _ = run_attention(ops, case, nq, nk, D, page, window, 1024, splits=splits)
+                close(got, ref, "bfloat16", rel16=0.02)
+                outs[kernel, splits] = got.float().cpu()
+    finally:
+        ops.attention_kernel = 0
+    ops.check_kernel_errors()
+    for splits in (1, 3, 7):
+        assert (outs[3, splits] - outs[2, splits]).abs().max() <= 0.02 * outs[2, splits].abs().max()
+
+
+def test_tma_fed_decode_ignores_rows_that_were_never_written(ops):
+    """The TMA-fed kernel copies whole tiles of 16 rows; rows at or beyond the context length may
+    hold any bits (here NaN and infinity) and must not reach the result."""
+    nq, nk, D, page = 4, 2, 64, 32
+    ctx_lens = [5, 40, 47, 200]
+    case = list(paged_case(4, [1] * 4, ctx_lens, nq, nk, D, page, torch.bfloat16, seed=9))
+    k_pages, v_pages, tables = case[1], case[2], case[3]
+    for s, ctx in enumerate(ctx_lens):
+        for pos in range(ctx, -(-ctx // page) * page):
+            pg, off = int(tables[s, pos // page]), pos % page
+            k_pages[pg, :, off] = float("nan")
+            v_pages[pg, :, off] = float("inf") if pos % 2 else float("nan")
+    try:
+        ops.attention_kernel = 3
+        for splits in (1, 2):
+            got, ref, _ = run_attention(ops, tuple(case), nq, nk, D, page, 0, 512, splits=splits)
+            assert torch.isfinite(got.float()).all()
+            close(got, ref, "bfloat16", rel16=0.02)
+    finally:
+        ops.attention_kernel = 0
+    ops.check_kernel_errors()
+
+
+@pytest.mark.parametrize("kernel", [2, 3])
 @pytest.mark.parametrize("group", [3, 8, 12])
-def test_grouped_decode_finds_one_far_key(ops, group):
+def test_grouped_decode_finds_one_far_key(ops, group, kernel):
     """One key among 900 wins every head's softmax; the output must be its value row."""
     nk, D, page, ctx = 2, 64, 16, 900
     nq = nk * group
@@ -369,7 +417,11 @@ def test_grouped_decode_finds_one_far_key(ops, group):
         else:
             k_pages[pg, :, off] = 0.0
             k_pages[pg, :, off, 3] = 30.0
-        got, ref, _ = run_attention(ops, tuple(case), nq, nk, D, page, 0, 1024, splits=3, rope=False)
+        try:
+            ops.attention_kernel = kernel  # 3 (TMA-fed) serves groups of up to 8; 12 falls to the other
+            got, ref, _ = run_attention(ops, tuple(case), nq, nk, D, page, 0, 1024, splits=3, rope=False)
+        finally:
+            ops.attention_kernel = 0
         close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
 
 

@@ -1464,12 +1464,15 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     const long long blocks = (long long)mgrid.x * mgrid.y * mgrid.z;
     const long long pool_rows = a->num_pages * a->num_kv_heads * a->page_tokens;
     // The TMA-fed kernel needs pages that hold whole tiles of 16 keys and the pool's size. It is
-    // the faster one for grids of many waves (head size 64, 2118 keys, alone: batch 64 159 us
-    // against 164, batch 48 133 against 143; in the whole step batch 64 gains 2.7 %), the
-    // register-fed one for grids of about one wave (batch 8: 27.3 us against 30.6; batch 32: 86
-    // against 89), where a block's start (barriers, descriptor fetch) is a larger share.
+    // the faster one where a block walks a whole context and the grid is several waves (head size
+    // 64, 32 heads, alone: 64 sequences of 2118 keys 160.8 us against 164.5, of 600 keys 51.0
+    // against 51.5; in the whole step batch 64 gains 2.7 %). A block's start costs more than the
+    // register-fed kernel's (barriers, descriptor fetch), so with partitions (shorter walks: 48
+    // sequences in 2 partitions 137 us against 130) and with grids of about one wave (batch 8 in 4
+    // partitions: 30.6 against 27.3) the other one is taken.
     const bool ring_can = G <= 8 && ps >= 4 && pool_rows > 0 && pool_rows < (1LL << 31);
-    if (ring_can && (a->force_simt == 3 || (a->force_simt == 0 && blocks >= 10LL * sms))) {
+    if (ring_can && (a->force_simt == 3 ||
+                     (a->force_simt == 0 && a->num_splits == 1 && blocks >= 10LL * sms))) {
       constexpr int PER = 1;
       constexpr int smem = PER * DEC_WARPS * 2 * ring::TILE_BYTES + 1024;
       static bool configured = false;
@@ -1523,6 +1526,34 @@ extern "C" size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, 
   // a fixed region of completion counters, then the partial results
   return num_splits > 1 ? (size_t)LSE_ATTN_COUNTERS + (size_t)num_decode * num_heads * num_splits * (D + 2)
                         : 0;
+}
+
+// Blocks of the single-token kernel for these head counts that one SM holds at a time (0 if it
+// cannot be asked): what the choice of the number of context partitions rests on.
+template <typename K>
+static int blocks_per_sm(K kernel) {
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, DEC_WARPS * 32, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+extern "C" int lse_attn_decode_blocks_per_sm(int dtype, int num_heads, int num_kv_heads) {
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return 0;
+  const int G = num_heads / num_kv_heads;
+#if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
+  if (dtype == LSE_BF16 && G <= 8) return blocks_per_sm(decode_mma8_kernel<false>);
+#endif
+#if LSE_HEAD_DIM == 64
+  if (dtype == LSE_BF16 && G <= 16) return blocks_per_sm(decode_mma_kernel);
+#endif
+  const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
+  if (dtype == LSE_BF16)
+    return gt == 1 ? blocks_per_sm(decode_split_kernel<bf16, 1>)
+                   : gt == 2 ? blocks_per_sm(decode_split_kernel<bf16, 2>) : blocks_per_sm(decode_split_kernel<bf16, 4>);
+  return gt == 1 ? blocks_per_sm(decode_split_kernel<float, 1>)
+                 : gt == 2 ? blocks_per_sm(decode_split_kernel<float, 2>) : blocks_per_sm(decode_split_kernel<float, 4>);
 }
 
 extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {

@@ -50,6 +50,8 @@ int lse_attn_head_dim(void);
 // rows per tile that lse_attn_prefill expects in `tiles` for this dtype
 int lse_attn_q_tile(int dtype);
 size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, int num_splits);
+// blocks of lse_attn_decode's kernel for these head counts that one SM holds at a time; 0: unknown
+int lse_attn_decode_blocks_per_sm(int dtype, int num_heads, int num_kv_heads);
 // The kernels of both launchers are enqueued with programmatic stream serialization and read the
 // batch description (`tiles`, `decode_seqs`, `cu_q`, `ctx_lens`) *before* their dependency wait.
 // Those four arrays must therefore be complete before the call is enqueued (a host-to-device copy

@@ -244,6 +244,7 @@ struct AttnLib {
   int (*head_dim)(void);
   int (*q_tile)(int);
   size_t (*scratch_floats)(int, int, int);
+  int (*decode_blocks_per_sm)(int, int, int);
   int (*prefill)(const LseAttnArgs*, cudaStream_t);
   int (*decode)(const LseAttnArgs*, cudaStream_t);
 };
@@ -261,9 +262,11 @@ void load_attention_library(const std::string& path, int64_t head_dim) {
   lib.head_dim = (int (*)(void))dlsym(h, "lse_attn_head_dim");
   lib.q_tile = (int (*)(int))dlsym(h, "lse_attn_q_tile");
   lib.scratch_floats = (size_t(*)(int, int, int))dlsym(h, "lse_attn_decode_scratch_floats");
+  lib.decode_blocks_per_sm = (int (*)(int, int, int))dlsym(h, "lse_attn_decode_blocks_per_sm");
   lib.prefill = (int (*)(const LseAttnArgs*, cudaStream_t))dlsym(h, "lse_attn_prefill");
   lib.decode = (int (*)(const LseAttnArgs*, cudaStream_t))dlsym(h, "lse_attn_decode");
-  TORCH_CHECK(lib.head_dim && lib.q_tile && lib.scratch_floats && lib.prefill && lib.decode,
+  TORCH_CHECK(lib.head_dim && lib.q_tile && lib.scratch_floats && lib.decode_blocks_per_sm && lib.prefill &&
+                  lib.decode,
               "attention library ", path, " lacks an entry point");
   TORCH_CHECK(lib.head_dim() == head_dim, "attention library ", path, " was built for head size ",
               num(lib.head_dim()), ", not ", num(head_dim));
@@ -283,6 +286,10 @@ int64_t attention_q_tile(int64_t D, bool bf16, int64_t force_kernel) {
 
 int64_t attention_scratch_floats(int64_t D, int64_t num_decode, int64_t num_heads, int64_t splits) {
   return (int64_t)attn_lib(D).scratch_floats((int)num_decode, (int)num_heads, (int)splits);
+}
+
+int64_t attention_decode_blocks_per_sm(int64_t D, bool bf16, int64_t num_heads, int64_t num_kv_heads) {
+  return attn_lib(D).decode_blocks_per_sm(bf16 ? LSE_BF16 : LSE_F32, (int)num_heads, (int)num_kv_heads);
 }
 
 // q: the fused projection [T, q_width_total] whose first num_heads*D columns are the queries, or
@@ -485,6 +492,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("load_attention_library", &load_attention_library);
   m.def("attention_q_tile", &attention_q_tile);
   m.def("attention_scratch_floats", &attention_scratch_floats);
+  m.def("attention_decode_blocks_per_sm", &attention_decode_blocks_per_sm);
   m.def("paged_attention", &paged_attention);
   m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
         py::arg("min_p"), py::arg("seed"), py::arg("draw"), py::arg("out"), py::arg("scratch") = py::none(),

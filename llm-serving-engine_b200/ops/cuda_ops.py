@@ -52,6 +52,44 @@ class PendingSums:
         return None
 
 
+# Cost of a block of the single-token attention kernel in units of one key: its start (tables,
+# queries, first tile) and end (partial results, counter), and what each further partition adds
+# to the merge. From timings at 2118 keys of head size 64: a wave of blocks takes about 39 ns per
+# key and 5 us besides.
+_BLOCK_START_KEYS = 130
+_MERGE_KEYS_PER_SPLIT = 4
+
+
+def choose_decode_splits(pairs: int, max_ctx: int, num_sms: int, blocks_per_sm: int) -> int:
+    """Context partitions per (sequence, key/value head) for ``pairs`` such pairs.
+
+    The kernel runs one block per (partition, pair); ``blocks_per_sm * num_sms`` of them run at a
+    time, a *wave*. One tile of keys is in flight per warp, so a block's speed is set by latency,
+    not by how many blocks share the SM, and a wave that is part empty takes as long as a full
+    one: 12 sequences x 32 heads cut in 3 make 1152 blocks for 1036 places and took 49 us where
+    24 sequences took 79. So the number of partitions is the one that minimises
+    ``waves * (keys per block + a block's fixed cost)``, among partitions of 128 keys or more
+    (measured at one sequence of 2176 keys: 8 partitions 13.3 us, 16 10.9, 28 11.9, 34 12.1).
+    The context is rounded up to a power of two first, so that the choice (which captured graphs
+    are keyed on) does not flicker from step to step. Without a known occupancy: about six blocks
+    per SM.
+    """
+    if pairs <= 0:
+        return 1
+    most = int(max(1, min((max_ctx + 127) // 128, 64)))
+    if blocks_per_sm <= 0:
+        want = max(1, (6 * num_sms + pairs - 1) // pairs)
+        return int(min(want, most))
+    wave = blocks_per_sm * num_sms
+    ctx = 1 << max(0, int(max_ctx) - 1).bit_length()
+
+    def cost(s: int) -> int:
+        waves = -(-pairs * s // wave)
+        return waves * (-(-ctx // s) + _BLOCK_START_KEYS + _MERGE_KEYS_PER_SPLIT * s)
+
+    return min(range(1, most + 1), key=lambda s: (cost(s), s))
+
+
 class CudaOps:
     name = "cuda-sm100a"
     defers_adds = True  # linear(..., accumulate_into=x, may_defer=True) may return PendingSums
@@ -65,6 +103,7 @@ class CudaOps:
         self.ext = build.load_core()
         self._attn_loaded: set[int] = set()
         self._scratch: torch.Tensor | None = None
+        self.decode_blocks_per_sm = 0  # of the single-token attention kernel; 0: not asked yet
         self._sample_scratch: torch.Tensor | None = None
         self._sample_rows = 0
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -85,12 +124,21 @@ class CudaOps:
         """Dtype in which projections that feed the residual stream return their result."""
         return torch.float32
 
-    def check_attention_shape(self, head_dim: int, dtype: torch.dtype) -> None:
+    def check_attention_shape(self, head_dim: int, dtype: torch.dtype, num_heads: int | None = None,
+                              num_kv_heads: int | None = None) -> None:
+        """Load the kernels of this head size. With the head counts given, also ask how many blocks
+        of the single-token kernel an SM holds (the smallest answer over a model's layers is kept:
+        :meth:`decode_splits` fills whole waves of that many blocks)."""
         if dtype not in _DTYPES:
             raise ValueError(f"attention kernels exist for float32 and bfloat16, not {dtype}")
         if head_dim not in self._attn_loaded:
             self.ext.load_attention_library(build.attention_library(head_dim), head_dim)
             self._attn_loaded.add(head_dim)
+        if num_heads and num_kv_heads:
+            n = int(self.ext.attention_decode_blocks_per_sm(head_dim, dtype == torch.bfloat16,
+                                                            num_heads, num_kv_heads))
+            if n > 0:
+                self.decode_blocks_per_sm = min(self.decode_blocks_per_sm or n, n)
 
     def reserve_attention_scratch(self, head_dim: int, max_decode: int, num_heads: int,
                                   max_splits: int = 64) -> None:
@@ -275,13 +323,8 @@ class CudaOps:
         }
 
     def decode_splits(self, num_decode, num_kv_heads, max_ctx):
-        """Context partitions per (sequence, head): about six blocks per SM, 128 keys or more each
-        (measured at one sequence of 2176 keys: 8 partitions 13.3 µs, 16 10.9, 28 11.9, 34 12.1)."""
-        if num_decode == 0:
-            return 1
-        blocks = num_decode * num_kv_heads
-        want = max(1, (6 * self.num_sms + blocks - 1) // blocks)
-        return int(max(1, min(want, (max_ctx + 127) // 128, 64)))
+        """Context partitions per (sequence, head) for a step of single tokens."""
+        return choose_decode_splits(num_decode * num_kv_heads, max_ctx, self.num_sms, self.decode_blocks_per_sm)
 
     def paged_attention(self, q, *, num_heads, num_kv_heads, head_dim, scale, window, k_pages,
                         v_pages, block_tables, page_tokens, step, plan):

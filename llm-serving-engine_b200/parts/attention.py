@@ -45,7 +45,7 @@ class PagedAttention(Mixer):
         self.kv_size = spec.num_kv_heads * spec.head_dim
         self.position = POSITION_ENCODINGS.build(spec.position, env)
         self.rotary = self.position.rotary_tables()
-        env.ops.check_attention_shape(spec.head_dim, env.dtype)
+        env.ops.check_attention_shape(spec.head_dim, env.dtype, spec.num_heads, spec.num_kv_heads)
 
     def param_decls(self):
         s = self.spec

@@ -41,7 +41,7 @@ class PlainOps:
     def branch_dtype(self, dtype):
         return torch.float32
 
-    def check_attention_shape(self, head_dim, dtype):
+    def check_attention_shape(self, head_dim, dtype, num_heads=None, num_kv_heads=None):
         if head_dim % 16:
             raise ValueError("head size must be a multiple of 16")
 

@@ -366,3 +366,29 @@ def test_a_kernel_that_gave_up_waiting_stops_the_engine(sharp_dirs):
     ops.code = 104
     with pytest.raises(RuntimeError, match="gave up waiting"):
         eng.step()
+
+
+def test_context_partitions_fill_whole_waves():
+    """148 SMs holding 7 blocks each run 1036 blocks at a time. The number of partitions per
+    (sequence, head) avoids a last wave that is nearly empty, keeps partitions of 128 keys or
+    more, and does not change while the context stays between two powers of two."""
+    from llmserve_b200.ops.cuda_ops import choose_decode_splits
+
+    def pick(batch, ctx=2118, heads=32):
+        return choose_decode_splits(batch * heads, ctx, 148, 7)
+
+    assert pick(1) == 17        # 544 blocks, partitions of 125 keys: as many as the 128-key rule allows
+    assert pick(8) == 4         # 1024 blocks: one wave
+    assert pick(12) in (2, 5)   # 768 or 1920 blocks, not 1152 (a second wave for 116 blocks)
+    assert pick(24) == 4        # 3072 blocks: three waves, not 1536 (one and a half)
+    assert pick(48) == 2        # 3072 blocks again
+    assert pick(64) == 1        # 2048 blocks: two waves
+    assert pick(8, ctx=100) == 1 and pick(8, ctx=300) <= 3
+    assert len({pick(24, ctx=c) for c in range(2049, 4097, 97)}) == 1
+    for batch in range(1, 70):
+        for ctx in (1, 127, 129, 1000, 5000, 70000):
+            s = pick(batch, ctx)
+            assert 1 <= s <= 64 and (s == 1 or (ctx + 127) // 128 >= s)
+    # occupancy unknown: about six blocks per SM, as before
+    assert choose_decode_splits(256, 2118, 148, 0) == 4
+    assert choose_decode_splits(0, 2118, 148, 7) == 1

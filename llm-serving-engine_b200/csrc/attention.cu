@@ -920,7 +920,14 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 
 // EARLY: the rows of the warp's first tile are loaded into registers before the dependency wait
 // (the registers stay live across it, which costs occupancy: for grids that do not fill the SMs).
-template <bool EARLY>
+// FUSED: the queries, and this step's key and value, are not read from q and the pages but made
+// here from the fixed-point sums of the fused q|k|v projection (a.qkv_sums): rotated at position
+// ctx - 1 and rounded to bfloat16, exactly what the rotation kernel would have stored. The block
+// whose partition ends at this step's token writes the new key and value into their page and adds
+// them to its result from shared memory (the tile loop stops one key earlier); the block that
+// finishes last for a (sequence, key/value head) clears the sums it stands for. This saves the
+// rotation kernel between the projection and the attention of a step of single tokens.
+template <bool EARLY, bool FUSED>
 __global__ void __launch_bounds__(DEC_WARPS * 32, EARLY ? 4 : 0)  // 0: no promise, the compiler's own choice
 decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   using T = bf16;
@@ -931,6 +938,8 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   constexpr int MT = D / 16;   // output tiles of 16 head dims
   __shared__ float sm_m[DEC_WARPS][HEADS], sm_l[DEC_WARPS][HEADS];
   __shared__ float sm_acc[DEC_WARPS][HEADS][D];
+  __shared__ __align__(16) T sm_q[FUSED ? HEADS * D : 8];  // rotated queries of the block's heads
+  __shared__ __align__(16) T sm_new[FUSED ? 2 * D : 8];    // this step's key, then its value
   pdl_trigger();
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -943,7 +952,10 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   const int span = ctx - k_first;
   const int per = (span + a.num_splits - 1) / a.num_splits;
   const int lo = k_first + split * per;
-  const int hi = min(ctx, lo + per);
+  const int hi_all = min(ctx, lo + per);
+  // FUSED: the partition that ends at this step's token takes that key from the sums, not the pages
+  const bool owns_new = FUSED && hi_all == ctx && hi_all > lo;
+  const int hi = owns_new ? hi_all - 1 : hi_all;  // keys [lo, hi) come from the pages
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -1013,6 +1025,50 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
 
   pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
 
+  if (FUSED) {
+    // one thread per rotation pair (i, i + D/2): the block's query heads, and in the block that
+    // owns this step's token its key (rotated) and value (as it is)
+    constexpr int HALF = D / 2;
+    const long long* row = a.qkv_sums + (size_t)tok * (a.num_heads + 2 * a.num_kv_heads) * D;
+    const int pos = ctx - 1;
+    const float* c = a.rope_cos ? a.rope_cos + (size_t)pos * HALF : nullptr;
+    const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * HALF : nullptr;
+    const int q_pairs = G * HALF;
+    const int pairs = q_pairs + (owns_new ? 2 * HALF : 0);
+    size_t page_base = 0;
+    if (owns_new) {
+      int pi, off;
+      page_of(pos, a.page_tokens, page_shift, pi, off);
+      page_base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
+    }
+    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+      const int what = idx < q_pairs ? 0 : (idx < q_pairs + HALF ? 1 : 2);  // query, key, value
+      const int head = what == 0 ? idx / HALF : 0;
+      const int i = what == 0 ? idx - head * HALF : (idx - q_pairs) - (what - 1) * HALF;
+      const size_t col = what == 0 ? (size_t)(h0 + head) * D
+                                   : (size_t)(a.num_heads + (what - 1) * a.num_kv_heads + kvh) * D;
+      float x1 = fixed_to_float(__ldcg(row + col + i)), x2 = fixed_to_float(__ldcg(row + col + i + HALF));
+      if (what != 2 && c) {
+        const float cv = c[i], sv = sn[i];
+        const float r1 = x1 * cv - x2 * sv, r2 = x2 * cv + x1 * sv;
+        x1 = r1;
+        x2 = r2;
+      }
+      const T b1 = __float2bfloat16(x1), b2 = __float2bfloat16(x2);
+      if (what == 0) {
+        sm_q[head * D + i] = b1;
+        sm_q[head * D + i + HALF] = b2;
+      } else {
+        sm_new[(what - 1) * D + i] = b1;
+        sm_new[(what - 1) * D + i + HALF] = b2;
+        T* dst = (what == 1 ? (T*)a.k_pages : (T*)a.v_pages) + page_base;
+        dst[i] = b1;
+        dst[i + HALF] = b2;
+      }
+    }
+    __syncthreads();
+  }
+
   // Q^T as the column operand: column g is head h0 + g (zero beyond the group); multiply step s
   // pairs logical k = 2t, 2t+1, 2t+8, 2t+9 with head dims d0 .. d0+3, d0 = 8 (t + 4 (s / 2)) +
   // 4 (s % 2), the dims that K's 16-byte pieces t and t + 4 supply.
@@ -1022,7 +1078,8 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
     const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
     qb[s][0] = qb[s][1] = 0;
     if (g < G) {
-      const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + g) * D + d0;
+      const T* q = FUSED ? sm_q + g * D + d0
+                         : (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + g) * D + d0;
       qb[s][0] = *reinterpret_cast<const uint32_t*>(q);
       qb[s][1] = *reinterpret_cast<const uint32_t*>(q + 2);
     }
@@ -1086,6 +1143,38 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
       }
     }
   }
+  if (FUSED && owns_new && warp == 0) {
+    // this step's own key, from shared memory: its scores for heads 2t and 2t + 1 (dims shared
+    // out over g), then one more step of the running softmax and of O^T
+    float corr[2], pn[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int head = 2 * t + e;
+      float dot = 0.f;
+      if (head < G)
+        for (int d = g; d < D; d += 8) dot += __bfloat162float(sm_q[head * D + d]) * __bfloat162float(sm_new[d]);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 8);
+      dot += __shfl_xor_sync(0xffffffffu, dot, 16);
+      const float sc_new = head < G ? dot * a.scale : -INFINITY;
+      const float mx = fmaxf(m_run[e], sc_new);
+      const float m_fin = (mx == -INFINITY) ? 0.f : mx;
+      corr[e] = Exp<T>::f(m_run[e] - m_fin);
+      const float p = Exp<T>::f(sc_new - m_fin);
+      m_run[e] = mx;
+      l_run[e] = l_run[e] * corr[e] + (g == 0 ? p : 0.f);  // the warp's sum is joined over g below
+      pn[e] = __bfloat162float(__float2bfloat16(p));     // weights meet values as bfloat16, as in the tiles
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const int dim = 8 * (g + 8 * (i >> 2)) + 2 * (i & 3);
+      const float v0 = __bfloat162float(sm_new[D + dim]), v1 = __bfloat162float(sm_new[D + dim + 1]);
+      ot[i][0] = ot[i][0] * corr[0] + pn[0] * v0;
+      ot[i][1] = ot[i][1] * corr[1] + pn[1] * v0;
+      ot[i][2] = ot[i][2] * corr[0] + pn[0] * v1;
+      ot[i][3] = ot[i][3] * corr[1] + pn[1] * v1;
+    }
+  }
   // this warp's result in shared memory, head dims back in their places
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -1135,7 +1224,22 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
       }
     }
   }
-  if (a.num_splits == 1) return;
+  // FUSED: the sums that this (sequence, key/value head) stands for are cleared by the block after
+  // which no block reads them: the only one, or the one that finishes last (every other block
+  // read them before it counted itself done).
+  auto clear_sums = [&]() {
+    long long* row = const_cast<long long*>(a.qkv_sums) + (size_t)tok * (a.num_heads + 2 * a.num_kv_heads) * D;
+    for (int idx = threadIdx.x; idx < (G + 2) * D; idx += blockDim.x) {
+      const int part = idx / D, d = idx - part * D;
+      const size_t col = part < G ? (size_t)(h0 + part) * D
+                                  : (size_t)(a.num_heads + (part - G) * a.num_kv_heads + kvh) * D;
+      row[col + d] = 0;
+    }
+  };
+  if (a.num_splits == 1) {
+    if (FUSED) clear_sums();
+    return;
+  }
   __shared__ int is_last;
   __threadfence();
   __syncthreads();
@@ -1148,6 +1252,7 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  if (FUSED) clear_sums();
   merge_partitions<T, HEADS>(
       a.scratch + LSE_ATTN_COUNTERS + ((size_t)b * a.num_heads + h0) * a.num_splits * (D + 2),
       a.num_splits, G, (T*)a.out + (size_t)tok * a.out_row_stride + (size_t)h0 * D);
@@ -1436,7 +1541,7 @@ static int shift_of(int n) {
 static bool args_ok(const LseAttnArgs* a) {
   return a && (a->dtype == LSE_F32 || a->dtype == LSE_BF16) && a->num_heads > 0 &&
          a->num_kv_heads > 0 && a->num_heads % a->num_kv_heads == 0 && a->page_tokens > 0 &&
-         a->window >= 0 && a->q && a->out && a->k_pages && a->v_pages && a->block_tables &&
+         a->window >= 0 && (a->q || a->qkv_sums) && a->out && a->k_pages && a->v_pages && a->block_tables &&
          a->ctx_lens && a->cu_q;
 }
 
@@ -1471,7 +1576,8 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     // sequences in 2 partitions 137 us against 130) and with grids of about one wave (batch 8 in 4
     // partitions: 30.6 against 27.3) the other one is taken.
     const bool ring_can = G <= 8 && ps >= 4 && pool_rows > 0 && pool_rows < (1LL << 31);
-    if (ring_can && (a->force_simt == 3 ||
+    if (a->qkv_sums && G > 8) return LSE_BAD_ARGUMENT;  // only the kernel for groups of up to 8 makes its own queries
+    if (ring_can && !a->qkv_sums && (a->force_simt == 3 ||
                      (a->force_simt == 0 && a->num_splits == 1 && blocks >= 10LL * sms))) {
       constexpr int PER = 1;
       constexpr int smem = PER * DEC_WARPS * 2 * ring::TILE_BYTES + 1024;
@@ -1492,8 +1598,13 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     if (G <= 8) {
       // a grid that leaves the SMs part empty can afford the registers of an early first tile
       const bool small = blocks <= 4LL * sms;
-      if (small) launch(decode_mma8_kernel<true>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
-      else launch(decode_mma8_kernel<false>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+      if (a->qkv_sums) {
+        if (small) launch(decode_mma8_kernel<true, true>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+        else launch(decode_mma8_kernel<false, true>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+      } else {
+        if (small) launch(decode_mma8_kernel<true, false>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+        else launch(decode_mma8_kernel<false, false>, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
+      }
     }
 #if LSE_HEAD_DIM == 64
     else launch(decode_mma_kernel, mgrid, DEC_WARPS * 32, 0, stream, *a, ps);
@@ -1501,6 +1612,7 @@ static int launch_decode(const LseAttnArgs* a, cudaStream_t stream) {
     return cudaPeekAtLastError() == cudaSuccess ? LSE_OK : LSE_LAUNCH_FAILED;
   }
 #endif
+  if (a->qkv_sums) return LSE_BAD_ARGUMENT;  // the kernels below read their queries from q
   const int gt = G == 1 ? 1 : (G == 2 ? 2 : 4);
   dim3 grid(a->num_splits, a->num_kv_heads * ((G + gt - 1) / gt), a->num_decode);
   if (grid.y > 65535 || grid.z > 65535) return LSE_BAD_ARGUMENT;
@@ -1543,7 +1655,7 @@ extern "C" int lse_attn_decode_blocks_per_sm(int dtype, int num_heads, int num_k
   if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads) return 0;
   const int G = num_heads / num_kv_heads;
 #if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
-  if (dtype == LSE_BF16 && G <= 8) return blocks_per_sm(decode_mma8_kernel<false>);
+  if (dtype == LSE_BF16 && G <= 8) return blocks_per_sm(decode_mma8_kernel<false, false>);
 #endif
 #if LSE_HEAD_DIM == 64
   if (dtype == LSE_BF16 && G <= 16) return blocks_per_sm(decode_mma_kernel);
@@ -1556,8 +1668,16 @@ extern "C" int lse_attn_decode_blocks_per_sm(int dtype, int num_heads, int num_k
                  : gt == 2 ? blocks_per_sm(decode_split_kernel<float, 2>) : blocks_per_sm(decode_split_kernel<float, 4>);
 }
 
+extern "C" int lse_attn_decode_takes_sums(int dtype, int num_heads, int num_kv_heads) {
+#if LSE_HEAD_DIM == 64 || LSE_HEAD_DIM == 128
+  return dtype == LSE_BF16 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && num_heads / num_kv_heads <= 8;
+#else
+  return 0;
+#endif
+}
+
 extern "C" int lse_attn_prefill(const LseAttnArgs* a, cudaStream_t stream) {
-  if (!args_ok(a) || (a->num_tiles > 0 && !a->tiles)) return LSE_BAD_ARGUMENT;
+  if (!args_ok(a) || !a->q || (a->num_tiles > 0 && !a->tiles)) return LSE_BAD_ARGUMENT;
   if (a->num_tiles <= 0) return LSE_OK;
   if (a->num_tiles > 65535) return LSE_BAD_ARGUMENT;
   const int ps = shift_of(a->page_tokens);

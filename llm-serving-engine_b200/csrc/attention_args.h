@@ -42,6 +42,16 @@ struct LseAttnArgs {
   long long num_rows;      // rows of q and out
   long long num_pages;     // pages in k_pages / v_pages
   int* error_flag;         // device-visible int that receives a code if a bounded wait ran out, or null
+  // Single tokens straight from the fused q|k|v projection (lse_attn_decode only; null: not used).
+  // qkv_sums: [rows, (num_heads + 2 num_kv_heads) D] fixed-point sums (LSE_FIXED64) of the projection
+  // of this step's rows, every row a single token of its sequence. The kernel then ignores `q`:
+  // it makes the queries, and this step's key and value, from the sums (rotated with rope_cos /
+  // rope_sin [max_pos, D/2] at position ctx - 1 unless those are null, rounded to the pages'
+  // type), writes the key and value into their page, and leaves the sums zero. Served where
+  // lse_attn_decode_takes_sums() says so.
+  const long long* qkv_sums;
+  const float* rope_cos;
+  const float* rope_sin;
 };
 
 #define LSE_ATTN_COUNTERS 65536  // words at the start of the scratch: one counter per (sequence, head group)
@@ -52,6 +62,8 @@ int lse_attn_q_tile(int dtype);
 size_t lse_attn_decode_scratch_floats(int num_decode, int num_heads, int num_splits);
 // blocks of lse_attn_decode's kernel for these head counts that one SM holds at a time; 0: unknown
 int lse_attn_decode_blocks_per_sm(int dtype, int num_heads, int num_kv_heads);
+// 1 if lse_attn_decode serves LseAttnArgs::qkv_sums for this type and these head counts
+int lse_attn_decode_takes_sums(int dtype, int num_heads, int num_kv_heads);
 // The kernels of both launchers are enqueued with programmatic stream serialization and read the
 // batch description (`tiles`, `decode_seqs`, `cu_q`, `ctx_lens`) *before* their dependency wait.
 // Those four arrays must therefore be complete before the call is enqueued (a host-to-device copy

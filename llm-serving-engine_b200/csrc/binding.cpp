@@ -245,6 +245,7 @@ struct AttnLib {
   int (*q_tile)(int);
   size_t (*scratch_floats)(int, int, int);
   int (*decode_blocks_per_sm)(int, int, int);
+  int (*decode_takes_sums)(int, int, int);
   int (*prefill)(const LseAttnArgs*, cudaStream_t);
   int (*decode)(const LseAttnArgs*, cudaStream_t);
 };
@@ -263,10 +264,11 @@ void load_attention_library(const std::string& path, int64_t head_dim) {
   lib.q_tile = (int (*)(int))dlsym(h, "lse_attn_q_tile");
   lib.scratch_floats = (size_t(*)(int, int, int))dlsym(h, "lse_attn_decode_scratch_floats");
   lib.decode_blocks_per_sm = (int (*)(int, int, int))dlsym(h, "lse_attn_decode_blocks_per_sm");
+  lib.decode_takes_sums = (int (*)(int, int, int))dlsym(h, "lse_attn_decode_takes_sums");
   lib.prefill = (int (*)(const LseAttnArgs*, cudaStream_t))dlsym(h, "lse_attn_prefill");
   lib.decode = (int (*)(const LseAttnArgs*, cudaStream_t))dlsym(h, "lse_attn_decode");
-  TORCH_CHECK(lib.head_dim && lib.q_tile && lib.scratch_floats && lib.decode_blocks_per_sm && lib.prefill &&
-                  lib.decode,
+  TORCH_CHECK(lib.head_dim && lib.q_tile && lib.scratch_floats && lib.decode_blocks_per_sm &&
+                  lib.decode_takes_sums && lib.prefill && lib.decode,
               "attention library ", path, " lacks an entry point");
   TORCH_CHECK(lib.head_dim() == head_dim, "attention library ", path, " was built for head size ",
               num(lib.head_dim()), ", not ", num(head_dim));
@@ -369,6 +371,85 @@ void paged_attention(const Tensor& q, Tensor& out, const Tensor& k_pages, const 
     }
     done(lib.decode(&a, stream()), "paged_attention (single tokens)");
   }
+}
+
+bool attention_takes_sums(int64_t D, bool bf16, int64_t num_heads, int64_t num_kv_heads) {
+  return attn_lib(D).decode_takes_sums(bf16 ? LSE_BF16 : LSE_F32, (int)num_heads, (int)num_kv_heads) != 0;
+}
+
+// Single tokens straight from the fixed-point sums of the fused q|k|v projection: rotation, cache
+// write and attention in one launch; the sums are left zero. Every row of `sums` is one sequence's
+// single token (row i belongs to sequence decode_seqs[i] through cu_q).
+void paged_attention_from_sums(Tensor& sums, Tensor& out, Tensor& k_pages, Tensor& v_pages,
+                               int64_t num_heads, int64_t num_kv_heads, int64_t D, double scale,
+                               int64_t window, const Tensor& block_tables, const Tensor& ctx_lens,
+                               const Tensor& cu_q, const Tensor& decode_seqs, int64_t num_splits,
+                               const OptTensor& scratch, const OptTensor& cos, const OptTensor& sin) {
+  const AttnLib& lib = attn_lib(D);
+  check_cuda(sums, "sums");
+  check_cuda(out, "out");
+  check_cuda(k_pages, "k_pages");
+  check_cuda(v_pages, "v_pages");
+  check_i32(block_tables, "block_tables");
+  check_i32(ctx_lens, "ctx_lens");
+  check_i32(cu_q, "cu_q");
+  check_i32(decode_seqs, "decode_seqs");
+  const int64_t T = sums.size(0);
+  TORCH_CHECK(sums.scalar_type() == torch::kInt64 && sums.dim() == 2 &&
+                  sums.size(1) == (num_heads + 2 * num_kv_heads) * D,
+              "paged_attention_from_sums: sums must be int64 [T, (heads + 2 kv_heads) * head_dim]");
+  TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && k_pages.scalar_type() == torch::kBFloat16 &&
+                  v_pages.scalar_type() == torch::kBFloat16,
+              "paged_attention_from_sums: out and pages must be bfloat16");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == T && out.size(1) == num_heads * D,
+              "paged_attention_from_sums: out must be [T, heads*head_dim]");
+  TORCH_CHECK(k_pages.dim() == 4 && k_pages.size(1) == num_kv_heads && k_pages.size(3) == D &&
+                  v_pages.sizes() == k_pages.sizes(),
+              "paged_attention_from_sums: pages must be [pages, kv_heads, page_tokens, head_dim]");
+  TORCH_CHECK(block_tables.dim() == 2 && cu_q.size(0) == ctx_lens.size(0) + 1 &&
+                  block_tables.size(0) >= ctx_lens.size(0) && decode_seqs.numel() == T,
+              "paged_attention_from_sums: per-sequence arrays disagree, or a row is not a single token");
+  TORCH_CHECK(lib.decode_takes_sums(LSE_BF16, (int)num_heads, (int)num_kv_heads),
+              "paged_attention_from_sums: not served for these head counts");
+  TORCH_CHECK(cos.has_value() == sin.has_value(), "paged_attention_from_sums: cos and sin go together");
+  LseAttnArgs a{};
+  a.dtype = LSE_BF16;
+  a.qkv_sums = reinterpret_cast<const long long*>(sums.data_ptr());
+  if (cos) {
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 2 && cos->size(1) == D / 2 && sin->sizes() == cos->sizes(),
+                "paged_attention_from_sums: cos and sin must be [positions, head_dim / 2]");
+    a.rope_cos = cos->data_ptr<float>();
+    a.rope_sin = sin->data_ptr<float>();
+  }
+  a.out = out.data_ptr();
+  a.out_row_stride = out.stride(0);
+  a.k_pages = k_pages.data_ptr();
+  a.v_pages = v_pages.data_ptr();
+  a.num_heads = (int)num_heads;
+  a.num_kv_heads = (int)num_kv_heads;
+  a.page_tokens = (int)k_pages.size(2);
+  a.window = (int)window;
+  a.scale = (float)scale;
+  a.block_tables = block_tables.data_ptr<int>();
+  a.table_stride = (int)block_tables.size(1);
+  a.ctx_lens = ctx_lens.data_ptr<int>();
+  a.cu_q = cu_q.data_ptr<int>();
+  a.num_rows = T;
+  a.num_pages = k_pages.size(0);
+  a.error_flag = error_flag();
+  a.decode_seqs = decode_seqs.data_ptr<int>();
+  a.num_decode = (int)T;
+  a.num_splits = (int)num_splits;
+  if (num_splits > 1) {
+    TORCH_CHECK(scratch.has_value(), "paged_attention_from_sums: num_splits > 1 needs scratch");
+    check_f32(*scratch, "scratch");
+    TORCH_CHECK((size_t)scratch->numel() >= lib.scratch_floats((int)T, (int)num_heads, (int)num_splits),
+                "paged_attention_from_sums: scratch too small");
+    a.scratch = scratch->data_ptr<float>();
+  }
+  if (T > 0) done(lib.decode(&a, stream()), "paged_attention_from_sums");
 }
 
 // ------------------------------------------------------------------ sampling
@@ -494,6 +575,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attention_scratch_floats", &attention_scratch_floats);
   m.def("attention_decode_blocks_per_sm", &attention_decode_blocks_per_sm);
   m.def("paged_attention", &paged_attention);
+  m.def("paged_attention_from_sums", &paged_attention_from_sums);
+  m.def("attention_takes_sums", &attention_takes_sums);
   m.def("sample", &sample, py::arg("logits"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"),
         py::arg("min_p"), py::arg("seed"), py::arg("draw"), py::arg("out"), py::arg("scratch") = py::none(),
         py::arg("which") = 3);

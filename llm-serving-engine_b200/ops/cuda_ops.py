@@ -104,6 +104,8 @@ class CudaOps:
         self._attn_loaded: set[int] = set()
         self._scratch: torch.Tensor | None = None
         self.decode_blocks_per_sm = 0  # of the single-token attention kernel; 0: not asked yet
+        self.fuse_rotation_into_attention = True  # single tokens: attention makes q, k, v from the product's sums
+        self._takes_sums_known: dict[tuple, bool] = {}
         self._sample_scratch: torch.Tensor | None = None
         self._sample_rows = 0
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -291,6 +293,49 @@ class CudaOps:
             self._sums_taken(sums)
             return q
         return self.rope_kv_write(self.linear(h, w, bias), **kw)
+
+    def project_attend(self, h, w, bias, *, num_heads, num_kv_heads, head_dim, scale, window, positions,
+                       token_seq, cos, sin, k_pages, v_pages, writes, block_tables, page_tokens, step,
+                       plan, out_dtype):
+        """The fused q|k|v projection of ``h``, rotation, cache write (if ``writes``) and attention
+        over the cache. For a step of few single tokens in bfloat16 this is two launches: the
+        product leaves fixed-point sums, and the attention kernel makes its queries and this
+        step's key and value from them (a single token's position is its context length - 1).
+        Otherwise: projection, rotation + cache write, attention."""
+        T = h.shape[0]
+        n_dec = int(plan["decode_seqs"].shape[0])
+        if (self.fuse_rotation_into_attention and writes and n_dec == T and int(plan["tiles"].shape[0]) == 0
+                and self._few_rows(h, w) and out_dtype == torch.bfloat16 and self.attention_kernel in (0, 2)
+                and self._takes_sums(head_dim, num_heads, num_kv_heads)):
+            sums = self._product_sums(h, w, bias)
+            out = torch.empty(T, num_heads * head_dim, dtype=out_dtype, device=h.device)
+            splits = step.decode_splits if step.decode_splits else self.decode_splits(
+                n_dec, num_kv_heads, step.max_decode_ctx)
+            scratch = None
+            if splits > 1:
+                self.reserve_attention_scratch(head_dim, n_dec, num_heads, splits)
+                scratch = self._scratch
+            self.ext.paged_attention_from_sums(
+                sums, out, k_pages, v_pages, num_heads, num_kv_heads, head_dim, float(scale), int(window),
+                block_tables, step.ctx_lens, step.cu_q, plan["decode_seqs"], splits, scratch, cos, sin)
+            self._sums_taken(sums)
+            self.launches += 1
+            return out
+        q = self.project_rope_kv_write(
+            h, w, bias, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+            positions=positions, token_seq=token_seq, cos=cos, sin=sin,
+            k_pages=k_pages if writes else None, v_pages=v_pages if writes else None,
+            block_tables=block_tables, page_tokens=page_tokens, out_dtype=out_dtype)
+        return self.paged_attention(
+            q, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window,
+            k_pages=k_pages, v_pages=v_pages, block_tables=block_tables, page_tokens=page_tokens,
+            step=step, plan=plan)
+
+    def _takes_sums(self, head_dim, num_heads, num_kv_heads) -> bool:
+        key = (head_dim, num_heads, num_kv_heads)
+        if key not in self._takes_sums_known:
+            self._takes_sums_known[key] = bool(self.ext.attention_takes_sums(head_dim, True, num_heads, num_kv_heads))
+        return self._takes_sums_known[key]
 
     # ------------------------------------------------------------------ attention
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,

@@ -96,33 +96,24 @@ class PagedAttention(Mixer):
         ops = self.ops
         tables = step.block_tables[cache.group]
         cos, sin = self.rotary if self.rotary is not None else (None, None)
-        q = ops.project_rope_kv_write(
+        o = ops.project_attend(
             h, self.qkv_weight, self.qkv_bias,
-            num_heads=s.num_heads,
-            num_kv_heads=s.num_kv_heads,
-            head_dim=s.head_dim,
-            positions=step.positions,
-            token_seq=step.token_seq,
-            cos=cos,
-            sin=sin,
-            k_pages=cache.k if cache.writes else None,
-            v_pages=cache.v if cache.writes else None,
-            block_tables=tables,
-            page_tokens=cache.page_tokens,
-            out_dtype=self.env.dtype,
-        )
-        o = ops.paged_attention(
-            q,
             num_heads=s.num_heads,
             num_kv_heads=s.num_kv_heads,
             head_dim=s.head_dim,
             scale=s.scale,
             window=s.window,
+            positions=step.positions,
+            token_seq=step.token_seq,
+            cos=cos,
+            sin=sin,
             k_pages=cache.k,
             v_pages=cache.v,
+            writes=cache.writes,
             block_tables=tables,
             page_tokens=cache.page_tokens,
             step=step,
             plan=step.plans[self.plan_key()],
+            out_dtype=self.env.dtype,
         )
         return project_into(ops, o, self.o_weight, self.o_bias, self.env.residual_dtype, residual, may_defer)

@@ -82,6 +82,18 @@ class PlainOps:
         qkv = self.linear(h, w, bias, out_dtype=torch.float32)
         return self.rope_kv_write(qkv, out_dtype=out_dtype or h.dtype, **kw)
 
+    def project_attend(self, h, w, bias, *, num_heads, num_kv_heads, head_dim, scale, window, positions,
+                       token_seq, cos, sin, k_pages, v_pages, writes, block_tables, page_tokens, step,
+                       plan, out_dtype=None):
+        q = self.project_rope_kv_write(
+            h, w, bias, out_dtype=out_dtype, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim,
+            positions=positions, token_seq=token_seq, cos=cos, sin=sin, k_pages=k_pages if writes else None,
+            v_pages=v_pages if writes else None, block_tables=block_tables, page_tokens=page_tokens)
+        return self.paged_attention(
+            q, num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window,
+            k_pages=k_pages, v_pages=v_pages, block_tables=block_tables, page_tokens=page_tokens, step=step,
+            plan=plan)
+
     def rope_kv_write(self, qkv, *, num_heads, num_kv_heads, head_dim, positions, token_seq,
                       cos, sin, k_pages, v_pages, block_tables, page_tokens, out_dtype=None):
         T, D = qkv.shape[0], head_dim

@@ -291,6 +291,62 @@ def run_attention(ops, case, nq, nk, D, page, window, max_pos, theta=10000.0, sp
     return got, ref, (q_g, q_ref, kp_g, kp_ref, vp_g, vp_ref)
 
 
+@pytest.mark.parametrize("window,splits", [(0, 0), (0, 1), (0, 5), (40, 3)])
+@pytest.mark.parametrize("nq,nk,D,page,bias,rope", [(4, 4, 64, 16, False, True), (8, 2, 64, 8, True, True),
+                                                    (8, 1, 64, 64, False, False), (4, 2, 128, 16, True, True),
+                                                    (32, 32, 64, 16, False, True)])
+def test_projection_rotation_cache_write_and_attention_in_two_launches(ops, nq, nk, D, page, bias, rope,
+                                                                       window, splits):
+    """A step of single tokens: the product leaves fixed-point sums and the attention kernel makes
+    its queries and the step's key and value from them. Contexts from the new token alone to
+    several partitions; the pages must end up as after the separate rotation kernel, the output
+    must match the plain product, rotation and attention, and the sums must be left zero."""
+    K = 136
+    ctx_lens = [1, 2, 16, 17, 33, 130, 700, 64]
+    n = len(ctx_lens)
+    _, kp, vp, tables, positions, token_seq, step = paged_case(n, [1] * n, ctx_lens, nq, nk, D, page,
+                                                               torch.bfloat16, seed=nq + page)
+    h = rnd(n, K, dtype=torch.bfloat16, seed=5)
+    w = rnd((nq + 2 * nk) * D, K, dtype=torch.bfloat16, seed=6, scale=0.1)
+    b = rnd((nq + 2 * nk) * D, dtype=torch.bfloat16, seed=7) if bias else None
+    ang = torch.outer(torch.arange(720, dtype=torch.float64), 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float64) / D)))
+    cos, sin = (ang.cos().float(), ang.sin().float()) if rope else (None, None)
+    kw = dict(num_heads=nq, num_kv_heads=nk, head_dim=D, scale=D**-0.5, window=window, writes=True,
+              page_tokens=page, out_dtype=torch.bfloat16)
+    kp_ref, vp_ref = kp.clone(), vp.clone()
+    ref = PlainOps().project_attend(h, w, b, positions=positions, token_seq=token_seq, cos=cos, sin=sin,
+                                    k_pages=kp_ref, v_pages=vp_ref, block_tables=tables, step=step,
+                                    plan=None, **kw)
+    dev = lambda t: None if t is None else t.cuda()
+    ops.check_attention_shape(D, torch.bfloat16)
+    kp_g, vp_g = kp.cuda(), vp.cuda()
+    gstep = SimpleNamespace(cu_q=step.cu_q.cuda(), ctx_lens=step.ctx_lens.cuda(), decode_splits=splits,
+                            max_decode_ctx=step.max_decode_ctx)
+    plan = {k: torch.from_numpy(v).cuda() for k, v in ops.attention_plan(step, torch.bfloat16, D).items()}
+    before = ops.launches
+    got = ops.project_attend(dev(h), dev(w), dev(b), positions=dev(positions), token_seq=dev(token_seq),
+                             cos=dev(cos), sin=dev(sin), k_pages=kp_g, v_pages=vp_g, block_tables=dev(tables),
+                             step=gstep, plan=plan, **kw)
+    assert ops.launches - before == 2
+    close(got, ref, "bfloat16", rel16=0.02)
+    close(kp_g, kp_ref, "bfloat16", rel16=0.005)
+    close(vp_g, vp_ref, "bfloat16", rel16=0.005)
+    sums = ops._sums[(n, (nq + 2 * nk) * D)]
+    assert int(sums.abs().max()) == 0, "the attention kernel must leave the product's sums zero"
+    # the same again through the separate kernels: the pages, written from the same sums, agree bit for bit
+    kp_2, vp_2 = kp.cuda(), vp.cuda()
+    try:
+        ops.fuse_rotation_into_attention = False
+        got_2 = ops.project_attend(dev(h), dev(w), dev(b), positions=dev(positions), token_seq=dev(token_seq),
+                                   cos=dev(cos), sin=dev(sin), k_pages=kp_2, v_pages=vp_2, block_tables=dev(tables),
+                                   step=gstep, plan=plan, **kw)
+    finally:
+        ops.fuse_rotation_into_attention = True
+    assert torch.equal(kp_2, kp_g) and torch.equal(vp_2, vp_g)
+    assert (got.float() - got_2.float()).abs().max() <= 0.02 * got_2.float().abs().max()
+    ops.check_kernel_errors()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nq,nk,D,page", [(4, 4, 64, 16), (6, 2, 48, 8), (8, 1, 128, 32), (5, 5, 16, 4), (3, 1, 80, 7)])
 def test_rope_kv_write_and_attention_mixed_batch(ops, dtype, nq, nk, D, page):

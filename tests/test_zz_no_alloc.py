@@ -33,6 +33,7 @@ class AttnArgs(ctypes.Structure):
         ("decode_seqs", ctypes.c_void_p), ("num_decode", ctypes.c_int), ("num_splits", ctypes.c_int),
         ("scratch", ctypes.c_void_p),
         ("num_rows", ctypes.c_longlong), ("num_pages", ctypes.c_longlong), ("error_flag", ctypes.c_void_p),
+        ("qkv_sums", ctypes.c_void_p), ("rope_cos", ctypes.c_void_p), ("rope_sin", ctypes.c_void_p),
     ]
 
 

@@ -67,6 +67,7 @@ class DeviceStep:
     decode_splits: int  # fixed number of context partitions, or 0 to let the kernels choose
     plans: dict[Any, dict[str, Any]]
     host: HostStep | None = None
+    every_row_wanted: bool = False  # logit_rows is 0, 1, ..., num_tokens - 1: the final norm need not gather
 
 
 def build_host_step(entries: Sequence[StepEntry], manager, vocab_size: int, max_positions: int) -> HostStep:

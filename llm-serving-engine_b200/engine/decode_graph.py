@@ -79,7 +79,7 @@ class _Graph:
             first_portion=view("first_portion"),
             block_tables=[self.dev[o : o + B * w].view(B, w) for o, w in self.table_off],
             logit_rows=ar[:B], num_tokens=B, num_seqs=B, num_logit_rows=B, max_decode_ctx=0,
-            decode_splits=splits, plans=plans, host=None,
+            decode_splits=splits, plans=plans, host=None, every_row_wanted=True,
         )
         f32 = lambda name: view(name).view(torch.float32)
         so = self.off["seed"]

@@ -168,6 +168,8 @@ class ModelRunner:
             num_logit_rows=int(host.logit_rows.shape[0]),
             max_decode_ctx=int(host.ctx_lens[dec].max()) if dec.any() else 0,
             decode_splits=decode_splits, plans=plans, host=host,
+            every_row_wanted=bool(host.logit_rows.shape[0] == host.num_tokens
+                                  and np.array_equal(host.logit_rows, np.arange(host.num_tokens))),
         )
 
     # ------------------------------------------------------------------ the step

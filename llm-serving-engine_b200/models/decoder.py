@@ -123,7 +123,8 @@ class DecoderModel:
             if hasattr(pending, "resolve"):
                 pending.resolve()  # nobody reads x any more, but the kernel set's sums must be taken
             return torch.empty(0, self.plan.vocab_size, dtype=torch.float32, device=x.device)
-        h = self.final_norm.forward(x, settle(pending, self.final_norm), rows=step.logit_rows)
+        rows = None if step.every_row_wanted else step.logit_rows
+        h = self.final_norm.forward(x, settle(pending, self.final_norm), rows=rows)
         logits = self.ops.linear(h, self.head_weight, None, out_dtype=torch.float32)
         if self.plan.logit_scale != 1.0:
             logits *= self.plan.logit_scale

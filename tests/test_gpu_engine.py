@@ -76,6 +76,29 @@ def test_graphs_portions_and_preemption_give_the_same_tokens(sharp_dirs):
     assert tight.engine.stats()["kernel_set"] == "cuda-sm100a"
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_preemption_in_bfloat16_with_captured_steps(sharp_dirs, name):
+    """So few pages that requests are evicted and computed again, with captured steps of single
+    tokens and of portions, in the precision that is served: the tokens are those of a roomy
+    engine, up to a near-tie where a recomputed prompt meets other kernels (portions where the
+    first pass decoded), and no page is lost."""
+    pt = TINY[name]["page_tokens"]
+    prompts = PROMPTS[:4]
+    new = 2 * pt + 3  # every request outgrows the pages of its prompt twice
+    roomy = llm(sharp_dirs[name], name, "bfloat16", cuda_graphs=False)
+    want = [o.outputs[0].token_ids for o in roomy.generate(prompts, greedy(new))]
+    pages = sum(-(-len(p) // pt) for p in prompts) + 1  # all prompts fit, their growth does not
+    assert pages >= -(-(max(map(len, prompts)) + new) // pt)  # but each request alone does
+    tight = llm(sharp_dirs[name], name, "bfloat16", num_kv_blocks=pages, max_num_batched_tokens=16)
+    got = [o.outputs[0].token_ids for o in tight.generate(prompts, greedy(new))]
+    assert tight.engine.scheduler.num_preemptions > 0
+    for p, a, b in zip(prompts, got, want, strict=True):
+        assert_same_or_near_tie(sharp_dirs[name], p, a, b)
+    tight.engine.manager.check_invariants()
+    assert tight.engine.manager.usage() == 0.0
+    tight.engine.runner.ops.check_kernel_errors()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "C"])
 def test_captured_steps_with_portions_give_the_same_tokens(sharp_dirs, name, dtype):

@@ -499,13 +499,19 @@ def long_parity(layers: int) -> dict:
         runner = ModelRunner(model, page_tokens=16, num_pages=N // 16, max_model_len=N, max_num_seqs=2,
                              max_num_batched_tokens=N)
         got, a = [], 0
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
         for n in cuts:
             here = [r - a for r in rows if a <= r < a + n]
             logits = runner.run([StepEntry("x", ids[a : a + n], here)])
             if here:
                 got.append(logits.double().cpu())
             a += n
+        end.record()
+        torch.cuda.synchronize()
         out[f"float32_{name}_vs_plain_max_abs_diff"] = float((torch.cat(got) - want).abs().max())
+        # the true float32 path is the parity path (FFMA products, no tensor cores): its speed, for the record
+        out[f"float32_{name}_ms"] = round(start.elapsed_time(end), 1)
     return out
 
 

@@ -11,8 +11,8 @@ library-for-linear-layers split as the reference (src/llmserve/models/layers.py:
 The few-rows kernel shares a tile's K between blocks, which add their partial sums with integer
 atomics into a buffer of 64-bit fixed-point numbers (value * 2^24). Such sums have the same bits
 whatever the order of the additions was, so the bfloat16 path is reproducible from run to run.
-The kernel that consumes the product (rotation and cache write, SiLU, residual add and norm, or a
-plain conversion) reads the buffer, converts and leaves zeros behind. The buffers never leave
+The kernel that consumes the product (single-token attention, rotation and cache write, SiLU,
+residual add and norm, or a plain conversion) reads the buffer, converts and leaves zeros behind. The buffers never leave
 this class except as a :class:`PendingSums` that stands for "a product still to be added to the
 residual stream".
 """

@@ -407,6 +407,81 @@ def test_decode_over_long_contexts_at_large_batch(ops, batch, ctx, nq, nk):
     close(got, ref, "bfloat16", atol32=1e-5, rel16=0.02)
 
 
+@pytest.mark.parametrize("style", ["partial", "interleaved"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_rotations_are_a_permutation_and_a_table(ops, style, dtype):
+    """The kernels rotate the pairs (i, i + D/2) of a head with cos/sin [positions, D/2]. A rotation
+    of only the first R dims (pairs (i, i + R/2)) or of neighbouring dims (pairs (2i, 2i + 1)) is
+    the same computation after a fixed reordering of the head's dims in q and k (rows of the
+    projection, done once when weights are read: q . k does not change when both are reordered
+    alike) with cos = 1, sin = 0 in the table for the pairs that stay as they are. Shown here on
+    one sequence: prompt portion, then single tokens, against the rotation written out plainly."""
+    nq, nk, D, page, R = 4, 2, 64, 16, 32
+    n_prompt, n_new = 21, 3
+    n = n_prompt + n_new
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(n, nq, D, generator=g, dtype=torch.float64)
+    k = torch.randn(n, nk, D, generator=g, dtype=torch.float64)
+    v = torch.randn(n, nk, D, generator=g, dtype=torch.float64)
+    pos = torch.arange(n, dtype=torch.float64)
+    if style == "partial":
+        inv = 1.0 / (1e4 ** (torch.arange(0, R, 2, dtype=torch.float64) / R))
+        pairs = [(i, i + R // 2) for i in range(R // 2)]                   # rotated pairs, their angles inv[i]
+        rest = list(range(R, D))
+    else:
+        inv = 1.0 / (1e4 ** (torch.arange(0, D, 2, dtype=torch.float64) / D))
+        pairs = [(2 * i, 2 * i + 1) for i in range(D // 2)]
+        rest = []
+    ang = pos[:, None] * inv[None, :]                                       # [n, len(pairs)]
+
+    def rotate_plainly(x):
+        y = x.clone()
+        for j, (a, b) in enumerate(pairs):
+            c, s_ = ang[:, j].cos()[:, None], ang[:, j].sin()[:, None]
+            y[..., a] = x[..., a] * c - x[..., b] * s_
+            y[..., b] = x[..., b] * c + x[..., a] * s_
+        return y
+
+    qr, kr = rotate_plainly(q), rotate_plainly(k)
+    want = torch.zeros(n, nq, D, dtype=torch.float64)
+    for h in range(nq):
+        sc = (qr[:, h] @ kr[:, h // (nq // nk)].T) * D**-0.5
+        sc = sc.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
+        want[:, h] = sc.softmax(-1) @ v[:, h // (nq // nk)]
+    # the reordering: first halves of the pairs, then half of the untouched dims; then the second halves
+    order = [a for a, _ in pairs] + rest[: len(rest) // 2] + [b for _, b in pairs] + rest[len(rest) // 2 :]
+    assert sorted(order) == list(range(D))
+    cos = torch.ones(n, D // 2, dtype=torch.float64)
+    sin = torch.zeros(n, D // 2, dtype=torch.float64)
+    cos[:, : len(pairs)], sin[:, : len(pairs)] = ang.cos(), ang.sin()
+    dt = DT[dtype]
+    qkv = torch.cat([q[:, :, order].reshape(n, -1), k[:, :, order].reshape(n, -1), v.reshape(n, -1)], 1).to(dt)
+    ops.check_attention_shape(D, dt)
+    pages = -(-n // page) + 1
+    kp = torch.zeros(pages, nk, page, D, dtype=dt, device="cuda")
+    vp = torch.zeros_like(kp)
+    tables = torch.arange(pages, dtype=torch.int32).flip(0)[None].contiguous().cuda()
+    got = []
+    for a, b in [(0, n_prompt)] + [(i, i + 1) for i in range(n_prompt, n)]:
+        T = b - a
+        step = SimpleNamespace(cu_q=torch.tensor([0, T], dtype=torch.int32), ctx_lens=torch.tensor([b], dtype=torch.int32),
+                               q_lens=np.asarray([T], dtype=np.int32), decode_splits=0, max_decode_ctx=b if T == 1 else 0)
+        plan = {kk: torch.from_numpy(vv).cuda() for kk, vv in ops.attention_plan(step, dt, D).items()}
+        gstep = SimpleNamespace(cu_q=step.cu_q.cuda(), ctx_lens=step.ctx_lens.cuda(), decode_splits=0,
+                                max_decode_ctx=step.max_decode_ctx)
+        qg = ops.rope_kv_write(qkv[a:b].contiguous().cuda(), num_heads=nq, num_kv_heads=nk, head_dim=D,
+                               positions=torch.arange(a, b, dtype=torch.int32).cuda(),
+                               token_seq=torch.zeros(T, dtype=torch.int32).cuda(), cos=cos.float().cuda(),
+                               sin=sin.float().cuda(), k_pages=kp, v_pages=vp, block_tables=tables,
+                               page_tokens=page, out_dtype=dt)
+        got.append(ops.paged_attention(qg, num_heads=nq, num_kv_heads=nk, head_dim=D, scale=D**-0.5, window=0,
+                                       k_pages=kp, v_pages=vp, block_tables=tables, page_tokens=page,
+                                       step=gstep, plan=plan).double().cpu())
+    got = torch.cat(got).view(n, nq, D)
+    bound = 2e-5 if dtype == "float32" else 0.02 * float(want.abs().max())
+    assert (got - want).abs().max() <= bound, float((got - want).abs().max())
+
+
 @pytest.mark.parametrize("window", [0, 75])
 @pytest.mark.parametrize("nq,nk,D,page", [(4, 4, 64, 16), (8, 1, 64, 64), (6, 2, 64, 32), (8, 2, 128, 16), (3, 3, 128, 128)])
 def test_the_three_decode_kernels_agree(ops, nq, nk, D, page, window):

@@ -36,8 +36,12 @@ class KVGroupSpec:
     head_dim: int
     window: int  # 0: every token is kept
     page_tokens: int
+    dtype: object = None  # of the pages; None: the model's compute dtype
 
     def bytes_per_token(self, dtype_bytes: int) -> int:
+        """``dtype_bytes``: element size of the compute dtype (used unless the group names its own)."""
+        if self.dtype is not None:
+            dtype_bytes = self.dtype.itemsize
         return 2 * len(self.cache_ids) * self.num_kv_heads * self.head_dim * dtype_bytes
 
     def live_tokens(self, max_len: int, max_portion: int = 1) -> int:

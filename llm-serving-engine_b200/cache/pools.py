@@ -21,7 +21,8 @@ from .manager import KVGroupSpec, StateGroupSpec
 
 
 def group_cache_layers(needs: dict[int, object], page_tokens: int):
-    """Sort cache layers into key/value groups (same heads, head size and window) and state groups."""
+    """Sort cache layers into key/value groups (same heads, head size, window and page dtype) and
+    state groups."""
     kv: dict[tuple, list[int]] = {}
     st: dict[tuple, list[int]] = {}
     for cid in sorted(needs):
@@ -29,13 +30,13 @@ def group_cache_layers(needs: dict[int, object], page_tokens: int):
         if need is None:
             continue
         if isinstance(need, PagedKVNeed):
-            kv.setdefault((need.num_kv_heads, need.head_dim, need.window), []).append(cid)
+            kv.setdefault((need.num_kv_heads, need.head_dim, need.window, need.dtype), []).append(cid)
         elif isinstance(need, StateNeed):
             st.setdefault((tuple(need.shape), need.dtype), []).append(cid)
         else:
             raise TypeError(f"cache layer {cid}: unknown need {need!r}")
     kv_groups = [
-        KVGroupSpec(tuple(ids), nk, d, w, page_tokens) for (nk, d, w), ids in kv.items()
+        KVGroupSpec(tuple(ids), nk, d, w, page_tokens, dt) for (nk, d, w, dt), ids in kv.items()
     ]
     state_groups = [StateGroupSpec(tuple(ids), shape, dt) for (shape, dt), ids in st.items()]
     return kv_groups, state_groups
@@ -73,7 +74,7 @@ class CachePools:
         self.kv = [
             torch.zeros(
                 len(g.cache_ids), 2, n + 1, g.num_kv_heads, g.page_tokens, g.head_dim,
-                dtype=dtype, device=device,
+                dtype=g.dtype or dtype, device=device,
             )
             for g, n in zip(self.kv_groups, self.num_pages)
         ]

@@ -84,6 +84,7 @@ class PagedKVNeed:
     head_dim: int
     window: int = 0
     kind: str = "paged_kv"
+    dtype: object = None  # of the pages; None: the model's compute dtype (what the attention kernels here read)
 
 
 @dataclass(frozen=True)

@@ -148,3 +148,22 @@ def test_layers_are_grouped_by_what_they_keep():
     assert [g.cache_ids for g in st] == [(4,)]
     pages = pages_for_memory(kv, 64 << 20, 2, 4096, 512)
     assert pages[0] > pages[1] > 0  # the windowed group needs far fewer pages per request
+
+
+def test_a_part_may_ask_for_pages_of_another_dtype():
+    """Two mixers with the same heads but different page dtypes get groups (and pools) of their
+    own, and the memory split counts each group's own element size."""
+    import torch
+
+    from llmserve_b200.cache import CachePools, group_cache_layers, pages_for_memory
+    from llmserve_b200.parts.base import PagedKVNeed
+
+    needs = {0: PagedKVNeed(2, 16), 1: PagedKVNeed(2, 16, dtype=torch.float32), 2: PagedKVNeed(2, 16)}
+    kv, st = group_cache_layers(needs, 8)
+    assert [g.cache_ids for g in kv] == [(0, 2), (1,)] and not st
+    assert kv[0].bytes_per_token(2) == 2 * 2 * 2 * 16 * 2 and kv[1].bytes_per_token(2) == 2 * 1 * 2 * 16 * 4
+    pages = pages_for_memory(kv, 1 << 20, 2, 256, 64)
+    assert pages[0] == pages[1]  # the same bytes per token and the same live tokens: the same number of pages
+    pools = CachePools(kv, st, pages, 4, torch.bfloat16, "cpu")
+    assert pools.view(0, True).k.dtype == torch.bfloat16 and pools.view(1, True).k.dtype == torch.float32
+    assert pools.view(1, True).group == 1 and pools.view(2, False).group == 0

@@ -922,13 +922,15 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // (the registers stay live across it, which costs occupancy: for grids that do not fill the SMs).
 // FUSED: the queries, and this step's key and value, are not read from q and the pages but made
 // here from the fixed-point sums of the fused q|k|v projection (a.qkv_sums): rotated at position
-// ctx - 1 and rounded to bfloat16, exactly what the rotation kernel would have stored. The block
-// whose partition ends at this step's token writes the new key and value into their page and adds
-// them to its result from shared memory (the tile loop stops one key earlier); the block that
-// finishes last for a (sequence, key/value head) clears the sums it stands for. This saves the
+// ctx - 1 and rounded to bfloat16, exactly what the rotation kernel would have stored. Every thread
+// makes the query values of its own multiply operands. In the block whose partition ends at this
+// step's token, warp 0 writes the new key and value into their page and adds them to its result
+// from shared memory (the tile loop stops one key earlier); the block that finishes last for a
+// (sequence, key/value head) clears the sums it stands for. This saves the
 // rotation kernel between the projection and the attention of a step of single tokens.
 template <bool EARLY, bool FUSED>
-__global__ void __launch_bounds__(DEC_WARPS * 32, EARLY ? 4 : 0)  // 0: no promise, the compiler's own choice
+__global__ void __launch_bounds__(DEC_WARPS * 32, EARLY ? 4 : ((FUSED && D == 64) ? 7 : 0))  // 0: the compiler's own choice
+// (head size 64: 72 registers, 7 blocks per SM; the form that makes its own queries needs the promise to stay there)
 decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   using T = bf16;
   constexpr int HEADS = 8;
@@ -938,8 +940,7 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   constexpr int MT = D / 16;   // output tiles of 16 head dims
   __shared__ float sm_m[DEC_WARPS][HEADS], sm_l[DEC_WARPS][HEADS];
   __shared__ float sm_acc[DEC_WARPS][HEADS][D];
-  __shared__ __align__(16) T sm_q[FUSED ? HEADS * D : 8];  // rotated queries of the block's heads
-  __shared__ __align__(16) T sm_new[FUSED ? 2 * D : 8];    // this step's key, then its value
+  __shared__ __align__(16) T sm_new[FUSED ? 2 * D : 8];    // this step's key, then its value (warp 0's)
   pdl_trigger();
 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -1025,63 +1026,98 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
 
   pdl_wait();  // queries and this step's key/value rows come from the kernel before this one
 
-  if (FUSED) {
-    // one thread per rotation pair (i, i + D/2): the block's query heads, and in the block that
-    // owns this step's token its key (rotated) and value (as it is)
-    constexpr int HALF = D / 2;
-    const long long* row = a.qkv_sums + (size_t)tok * (a.num_heads + 2 * a.num_kv_heads) * D;
-    const int pos = ctx - 1;
-    const float* c = a.rope_cos ? a.rope_cos + (size_t)pos * HALF : nullptr;
-    const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * HALF : nullptr;
-    const int q_pairs = G * HALF;
-    const int pairs = q_pairs + (owns_new ? 2 * HALF : 0);
-    size_t page_base = 0;
-    if (owns_new) {
-      int pi, off;
-      page_of(pos, a.page_tokens, page_shift, pi, off);
-      page_base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
-    }
-    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
-      const int what = idx < q_pairs ? 0 : (idx < q_pairs + HALF ? 1 : 2);  // query, key, value
-      const int head = what == 0 ? idx / HALF : 0;
-      const int i = what == 0 ? idx - head * HALF : (idx - q_pairs) - (what - 1) * HALF;
-      const size_t col = what == 0 ? (size_t)(h0 + head) * D
-                                   : (size_t)(a.num_heads + (what - 1) * a.num_kv_heads + kvh) * D;
-      float x1 = fixed_to_float(__ldcg(row + col + i)), x2 = fixed_to_float(__ldcg(row + col + i + HALF));
-      if (what != 2 && c) {
-        const float cv = c[i], sv = sn[i];
-        const float r1 = x1 * cv - x2 * sv, r2 = x2 * cv + x1 * sv;
-        x1 = r1;
-        x2 = r2;
-      }
-      const T b1 = __float2bfloat16(x1), b2 = __float2bfloat16(x2);
-      if (what == 0) {
-        sm_q[head * D + i] = b1;
-        sm_q[head * D + i + HALF] = b2;
-      } else {
-        sm_new[(what - 1) * D + i] = b1;
-        sm_new[(what - 1) * D + i + HALF] = b2;
-        T* dst = (what == 1 ? (T*)a.k_pages : (T*)a.v_pages) + page_base;
-        dst[i] = b1;
-        dst[i + HALF] = b2;
-      }
-    }
-    __syncthreads();
-  }
-
   // Q^T as the column operand: column g is head h0 + g (zero beyond the group); multiply step s
   // pairs logical k = 2t, 2t+1, 2t+8, 2t+9 with head dims d0 .. d0+3, d0 = 8 (t + 4 (s / 2)) +
   // 4 (s % 2), the dims that K's 16-byte pieces t and t + 4 supply.
   uint32_t qb[KS][2];
+  if (FUSED) {
+    // The thread's dims are the 8-dim pieces t, t + 4, ... of head g: KS/2 pieces, of which the
+    // second half are the rotation partners (dim + D/2) of the first half, so every thread
+    // rotates what it needs from its own loads, and nothing goes through shared memory.
+    constexpr int HALF = D / 2, NPC = KS / 2;
+    const long long* row = a.qkv_sums + (size_t)tok * (a.num_heads + 2 * a.num_kv_heads) * D;
+    const int pos = ctx - 1;
+    const float* c = a.rope_cos ? a.rope_cos + (size_t)pos * HALF : nullptr;
+    const float* sn = a.rope_sin ? a.rope_sin + (size_t)pos * HALF : nullptr;
+    float x[NPC][8];
 #pragma unroll
-  for (int s = 0; s < KS; ++s) {
-    const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
-    qb[s][0] = qb[s][1] = 0;
+    for (int pc = 0; pc < NPC; ++pc)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[pc][e] = 0.f;
     if (g < G) {
-      const T* q = FUSED ? sm_q + g * D + d0
-                         : (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + g) * D + d0;
-      qb[s][0] = *reinterpret_cast<const uint32_t*>(q);
-      qb[s][1] = *reinterpret_cast<const uint32_t*>(q + 2);
+      const longlong2* src = reinterpret_cast<const longlong2*>(row + (size_t)(h0 + g) * D);
+#pragma unroll
+      for (int pc = 0; pc < NPC; ++pc) {
+        const int piece = t + 4 * pc;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const longlong2 v = __ldcg(src + piece * 4 + e);
+          x[pc][2 * e] = fixed_to_float(v.x);
+          x[pc][2 * e + 1] = fixed_to_float(v.y);
+        }
+      }
+      if (c) {
+#pragma unroll
+        for (int pc = 0; pc < NPC / 2; ++pc) {
+          const int i0 = 8 * (t + 4 * pc);  // first dim of the piece, below D/2
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float cv = c[i0 + e], sv = sn[i0 + e];
+            const float x1 = x[pc][e], x2 = x[pc + NPC / 2][e];
+            x[pc][e] = x1 * cv - x2 * sv;
+            x[pc + NPC / 2][e] = x2 * cv + x1 * sv;
+          }
+        }
+      }
+    }
+    // in the block that owns this step's token, warp 0 makes the new key (rotated) and value from
+    // the sums, writes them into their page and keeps them for itself (it adds that key after its tiles)
+    if (owns_new && warp == 0) {
+      int pi, off;
+      page_of(pos, a.page_tokens, page_shift, pi, off);
+      const size_t page_base = (((size_t)table[pi] * a.num_kv_heads + kvh) * a.page_tokens + off) * D;
+      const long long* ksrc = row + (size_t)(a.num_heads + kvh) * D;
+      const long long* vsrc = row + (size_t)(a.num_heads + a.num_kv_heads + kvh) * D;
+      for (int i = lane; i < HALF; i += 32) {
+        float k1 = fixed_to_float(__ldcg(ksrc + i)), k2 = fixed_to_float(__ldcg(ksrc + i + HALF));
+        const float v1 = fixed_to_float(__ldcg(vsrc + i)), v2 = fixed_to_float(__ldcg(vsrc + i + HALF));
+        if (c) {
+          const float cv = c[i], sv = sn[i];
+          const float r1 = k1 * cv - k2 * sv, r2 = k2 * cv + k1 * sv;
+          k1 = r1;
+          k2 = r2;
+        }
+        const T bk1 = __float2bfloat16(k1), bk2 = __float2bfloat16(k2);
+        const T bv1 = __float2bfloat16(v1), bv2 = __float2bfloat16(v2);
+        sm_new[i] = bk1;
+        sm_new[i + HALF] = bk2;
+        sm_new[D + i] = bv1;
+        sm_new[D + i + HALF] = bv2;
+        T* kd = (T*)a.k_pages + page_base;
+        T* vd = (T*)a.v_pages + page_base;
+        kd[i] = bk1;
+        kd[i + HALF] = bk2;
+        vd[i] = bv1;
+        vd[i + HALF] = bv2;
+      }
+      __syncwarp();
+    }
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      const int o = 4 * (s & 1);
+      qb[s][0] = pack_bf16(x[s >> 1][o], x[s >> 1][o + 1]);
+      qb[s][1] = pack_bf16(x[s >> 1][o + 2], x[s >> 1][o + 3]);
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
+      qb[s][0] = qb[s][1] = 0;
+      if (g < G) {
+        const T* q = (const T*)a.q + (size_t)tok * a.q_row_stride + (size_t)(h0 + g) * D + d0;
+        qb[s][0] = *reinterpret_cast<const uint32_t*>(q);
+        qb[s][1] = *reinterpret_cast<const uint32_t*>(q + 2);
+      }
     }
   }
   // O^T: tile i = 4 c + w (piece g + 8 c of the value rows, word w of the piece): rows g and g + 8
@@ -1146,17 +1182,25 @@ decode_mma8_kernel(const LseAttnArgs a, int page_shift) {
   if (FUSED && owns_new && warp == 0) {
     // this step's own key, from shared memory: its scores for heads 2t and 2t + 1 (dims shared
     // out over g), then one more step of the running softmax and of O^T
+    // q . k for head g over this thread's dims (its query registers), joined over t; heads 2t and
+    // 2t + 1, whose softmax state this thread keeps, are fetched from the lanes that hold them
+    float dot = 0.f;
+#pragma unroll
+    for (int s = 0; s < KS; ++s) {
+      const int d0 = 8 * (t + 4 * (s >> 1)) + 4 * (s & 1);
+      const __nv_bfloat162 q01 = *reinterpret_cast<const __nv_bfloat162*>(&qb[s][0]);
+      const __nv_bfloat162 q23 = *reinterpret_cast<const __nv_bfloat162*>(&qb[s][1]);
+      dot += __low2float(q01) * __bfloat162float(sm_new[d0]) + __high2float(q01) * __bfloat162float(sm_new[d0 + 1]) +
+             __low2float(q23) * __bfloat162float(sm_new[d0 + 2]) + __high2float(q23) * __bfloat162float(sm_new[d0 + 3]);
+    }
+    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
     float corr[2], pn[2];
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int head = 2 * t + e;
-      float dot = 0.f;
-      if (head < G)
-        for (int d = g; d < D; d += 8) dot += __bfloat162float(sm_q[head * D + d]) * __bfloat162float(sm_new[d]);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 8);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-      const float sc_new = head < G ? dot * a.scale : -INFINITY;
+      const float of_head = __shfl_sync(0xffffffffu, dot, 4 * head);
+      const float sc_new = head < G ? of_head * a.scale : -INFINITY;
       const float mx = fmaxf(m_run[e], sc_new);
       const float m_fin = (mx == -INFINITY) ? 0.f : mx;
       corr[e] = Exp<T>::f(m_run[e] - m_fin);

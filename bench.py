@@ -216,6 +216,51 @@ def measure_decode(engine, batch, steps, warmup, seed, check=False):
                 ctx_sum=ctx_sum, graph_vs_eager=diff)
 
 
+def step_timeline(engine, batch, seed) -> dict:
+    """Start and end of every kernel of one captured step of single tokens, from the framework's
+    profiler (CUPTI), summed by kernel: launches, time resident, and what the kernel adds to the
+    step (the time from the latest end of any kernel before it to its own end; a kernel that is
+    resident while the one before it still runs adds less than it lasts)."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    ids = start_decoding(engine, batch, seed)
+    for _ in range(4):
+        engine.step()
+    torch.cuda.synchronize()
+    graphs = engine.runner.decode_graphs.graphs
+    g = max((x for x in graphs.values() if x.batch == batch and x.slots == 0 and x.graph is not None
+             and x.sampled), key=lambda x: x.step.decode_splits)
+    for _ in range(3):
+        g.graph.replay()
+    torch.cuda.synchronize()
+    reps = 4
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(reps):
+            g.graph.replay()
+        torch.cuda.synchronize()
+    rows = sorted((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                  if e.device_type == torch.autograd.DeviceType.CUDA)
+    n = len(rows) // reps
+    step = rows[2 * n : 3 * n]  # the third replay
+    fam = collections.OrderedDict()
+    latest = step[0][0]
+    for start, end, name in step:
+        key = name.split("(")[0].replace("void ", "").replace("lse::", "")
+        f = fam.setdefault(key, {"launches": 0, "resident_us": 0.0, "adds_us": 0.0})
+        f["launches"] += 1
+        f["resident_us"] += end - start
+        f["adds_us"] += max(0.0, end - max(start, latest))
+        latest = max(latest, end)
+    for i in ids:
+        engine.abort_request(i)
+    out = {k: {a: (round(b, 1) if isinstance(b, float) else b) for a, b in v.items()}
+           for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["adds_us"])}
+    return {"step_us": round(latest - step[0][0], 1), "kernels": len(step), "by_kernel": out}
+
+
 def measure_prefill(engine, reps=5, warmup=3):
     import torch
 
@@ -338,6 +383,8 @@ def decode_main(args) -> int:
             by = nums["weight_bytes"] + r["ctx_sum"] * nums["kv_bytes_per_token"]
             pts[f"decode_b{b}_hbm_frac"] = round(by / (r["dev_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         line["points"] = pts
+    if args.timeline:
+        line["timeline"] = step_timeline(engine, args.batch, seed=3)
     if args.parity:
         del engine
         import torch
@@ -629,6 +676,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0 = all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 and prefill points")
+    ap.add_argument("--timeline", action="store_true",
+                    help="add what each kernel adds to a captured step (from the profiler; not a timing run)")
     ap.add_argument("--parity", action="store_true",
                     help="also compare a two-layer model of the same layer sizes with the plain implementation")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
